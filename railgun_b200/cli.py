@@ -147,15 +147,15 @@ def run_generate(args) -> int:
 
 def run_random_weights(args) -> int:
     from .config.base import read_json
-    from .config.registry import architecture_of
+    from .config.registry import architecture_name, architecture_of
     from .weights.random_init import write_random_model
 
     data = read_json(args.config)
-    archs = data.get("architectures") or []
-    if not archs:
-        print("error: the config has no 'architectures'", file=sys.stderr)
+    try:
+        arch = architecture_of(architecture_name(data, args.config))
+    except ValueError as e:
+        print(f"error: {e}", file=sys.stderr)
         return 2
-    arch = architecture_of(archs[0])
     out = write_random_model(arch.config_from_dict(data, args.config), args.seed, args.out, std=args.std)
     print(json.dumps({"written": str(out)}))
     return 0

@@ -53,14 +53,24 @@ def load_config(model_dir):
     """(Architecture, typed config) of a model folder, chosen by config.json."""
     path = Path(model_dir) / "config.json"
     data = read_json(path)
-    archs = data.get("architectures")
-    if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError(f"{path}: 'architectures' must be a non-empty list of names; "
-                          f"known: {known_architectures()}")
-    arch = architecture_of(archs[0])
+    arch = architecture_of(architecture_name(data, str(path)))
     return arch, arch.config_from_dict(data, str(path))
+
+
+def architecture_name(data: dict, where: str = "config.json") -> str:
+    """The name a config.json selects its model by: ``architectures[0]``, or
+    the string ``architecture``."""
+    archs = data.get("architectures")
+    if isinstance(archs, list) and archs and isinstance(archs[0], str):
+        return archs[0]
+    if archs is None and isinstance(data.get("architecture"), str):
+        return data["architecture"]
+    raise ConfigError(f"{where}: 'architectures' must be a non-empty list of names (or 'architecture' a name); "
+                      f"known: {known_architectures()}")
 
 
 def _ensure_builtin():
     if "LlamaForCausalLM" not in _ARCHITECTURES:
         from ..models import llama  # noqa: F401  (registers itself)
+    if "Dizatar" not in _ARCHITECTURES:
+        from ..models import dizatar  # noqa: F401

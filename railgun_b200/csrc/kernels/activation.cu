@@ -103,3 +103,18 @@ extern "C" int rg_silu_mul(const void* gu, void* out, int dtype, int T, int I, v
                          total);
     return RG_ERR_UNSUPPORTED;
 }
+
+// Soft cap of logits, in place: z <- cap * tanh(z / cap), 32-bit.
+__global__ void softcap_kernel(float* __restrict__ z, float cap, size_t n) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) z[i] = cap * tanhf(z[i] / cap);
+}
+
+extern "C" int rg_softcap(float* z, float cap, long long n, void* stream) {
+    if (n <= 0) return 0;
+    const int threads = 256;
+    return rg_launch(softcap_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0,
+                     (cudaStream_t)stream, 1, z, cap, (size_t)n);
+}

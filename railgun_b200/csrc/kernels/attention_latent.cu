@@ -1,0 +1,174 @@
+// Attention over a compressed ("latent") key/value cache.
+//
+// Every token keeps ONE vector for all heads: c (R numbers, RMS-normed) followed by a rotated key part
+// k_r (dr numbers).  A head's keys and values are linear in c (k = U_k c, v = U_v c), so the head never
+// expands them: with the query taken through U_k^T once (qa = [U_k^T q_plain | q_rot], D = R + dr numbers),
+//   score_j  = scale * qa . [c_j | k_r,j]
+//   out      = U_v (sum_j p_j c_j),   p = softmax over the visible keys
+// which makes all heads read the same cache rows: attention with one shared key/value "head" of size D whose
+// values are the first R numbers of the keys.  The products with U_k^T and U_v are batched matrix products
+// outside these kernels.
+//
+// Cache layout: [pages, page_size, D] rows, token slot = page * page_size + offset.
+//
+// Kernels here:
+//   latent_rope_cache    per token: RMS norm of the latent part and rotation of the shared key part into the
+//                        cache row; rotation of every head's rotated query part into qa[:, :, R:]
+//   latent_attention_general  one block per (token, head), all arithmetic in 32-bit, any sizes: the true
+//                        32-bit path and every shape the tensor-core kernels refuse
+#include "common.cuh"
+
+#define LAT_THREADS 128
+#define LAT_MAX_ACC 8            // output numbers per thread of the general kernel: R <= 8 * 128
+
+// Rotation of pairs (i, i + dims/2), i < dims/2, by the angle pos * freq[i], angle and functions in 32-bit;
+// numbers from `dims` on pass unchanged.  src and dst hold n numbers.
+template <typename A, typename B>
+__device__ __forceinline__ void rotate_pairs(const A* __restrict__ src, B* __restrict__ dst, int n, int dims,
+                                             const float* __restrict__ freq, float pos) {
+    const int half = dims >> 1;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float v;
+        if (i < half) {
+            const float a = pos * freq[i];
+            v = to_f32(src[i]) * cosf(a) - to_f32(src[i + half]) * sinf(a);
+        } else if (i < dims) {
+            const float a = pos * freq[i - half];
+            v = to_f32(src[i]) * cosf(a) + to_f32(src[i - half]) * sinf(a);
+        } else {
+            v = to_f32(src[i]);
+        }
+        dst[i] = from_f32<B>(v);
+    }
+}
+
+// proj: [T, ld] = per head [dn plain | dr rotated] query numbers, then at offset kv_off the down-projection
+// [R latent | dr key part].  qa: [T, H, R + dr]; only its last dr numbers per head are written here.
+template <typename A>
+__global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int kv_off, A* __restrict__ qa,
+                                         A* __restrict__ cache, const float* __restrict__ norm_w, float eps,
+                                         const float* __restrict__ freq, int rot_dims,
+                                         const int* __restrict__ positions, const int* __restrict__ slots,
+                                         int H, int dn, int dr, int R) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    const A* row = proj + (size_t)t * ld;
+    const int D = R + dr;
+    for (int h = 0; h < H; ++h)
+        rotate_pairs(row + (size_t)h * (dn + dr) + dn, qa + ((size_t)t * H + h) * D + R, dr, rot_dims, freq, pos);
+    const int slot = slots ? slots[t] : -1;
+    if (slot < 0) return;
+    const A* lat = row + kv_off;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) { const float v = to_f32(lat[i]); ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)R + eps);
+    A* dst = cache + (size_t)slot * D;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<A>(to_f32(lat[i]) * inv * norm_w[i]);
+    rotate_pairs(lat + R, dst + R, dr, rot_dims, freq, pos);
+}
+
+extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* qa, void* cache, int dtype,
+                                    const float* norm_w, float eps, const float* freq, int rot_dims,
+                                    const int* positions, const int* slots, int T, int H, int dn, int dr, int R,
+                                    void* stream) {
+    if (T <= 0) return 0;
+    if (rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || R < 1 || H < 1) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(LAT_THREADS), 0, s, 1, (const bf16*)proj, ld,
+                         kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(LAT_THREADS), 0, s, 1, (const float*)proj, ld,
+                         kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R);
+    return RG_ERR_UNSUPPORTED;
+}
+
+// qa: [T, H, D]; out: [T, H, R]; cache: [pages * page_size, D]; block_table: [requests, max_blocks].
+// A query at position p of request r sees the keys of r at positions [max(0, p - window + 1), p].
+template <typename A>
+__global__ void latent_attention_general_kernel(
+        const A* __restrict__ qa, A* __restrict__ out, const A* __restrict__ cache,
+        const int* __restrict__ block_table, int max_blocks, const int* __restrict__ req_of_token,
+        const int* __restrict__ positions, int H, int R, int D, int page_size, int window, float scale) {
+    extern __shared__ float smem[];
+    float* qs = smem;                    // [D]
+    float* ps = qs + D;                  // [LAT_THREADS]
+    float* scratch = ps + LAT_THREADS;   // [33]
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int r = req_of_token[t];
+    const int pos = positions[t];
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int* bt = block_table + (size_t)r * max_blocks;
+    const A* qrow = qa + ((size_t)t * H + h) * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) qs[i] = to_f32(qrow[i]) * scale;
+    __syncthreads();
+
+    float m = -INFINITY, l = 0.f;
+    float acc[LAT_MAX_ACC];
+#pragma unroll
+    for (int k = 0; k < LAT_MAX_ACC; ++k) acc[k] = 0.f;
+    for (int base = lo; base <= pos; base += LAT_THREADS) {
+        const int j = base + threadIdx.x;
+        float s = -INFINITY;
+        if (j <= pos) {
+            const A* krow = cache + ((size_t)bt[j / page_size] * page_size + j % page_size) * D;
+            float dot = 0.f;
+            for (int i = 0; i < D; ++i) dot += qs[i] * to_f32(krow[i]);
+            s = dot;
+        }
+        const float m_new = fmaxf(m, block_max(s, scratch));
+        const float p = (j <= pos) ? expf(s - m_new) : 0.f;
+        const float alpha = expf(m - m_new);           // 0 when m = -inf
+        l = l * alpha + block_sum(p, scratch);
+        m = m_new;
+        ps[threadIdx.x] = p;
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < LAT_MAX_ACC; ++k) acc[k] *= alpha;
+        const int n = min(LAT_THREADS, pos - base + 1);
+        for (int kk = 0; kk < n; ++kk) {
+            const int jj = base + kk;
+            const A* vrow = cache + ((size_t)bt[jj / page_size] * page_size + jj % page_size) * D;
+            const float pk = ps[kk];
+#pragma unroll
+            for (int k = 0; k < LAT_MAX_ACC; ++k) {
+                const int i = threadIdx.x + k * LAT_THREADS;
+                if (i < R) acc[k] += pk * to_f32(vrow[i]);
+            }
+        }
+        __syncthreads();
+    }
+    A* orow = out + ((size_t)t * H + h) * R;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int k = 0; k < LAT_MAX_ACC; ++k) {
+        const int i = threadIdx.x + k * LAT_THREADS;
+        if (i < R) orow[i] = from_f32<A>(acc[k] * inv);
+    }
+}
+
+extern "C" int rg_latent_attention_general(
+        const void* qa, void* out, const void* cache, int dtype, const int* block_table, int max_blocks,
+        const int* req_of_token, const int* positions, int T, int H, int R, int D, int page_size, int window,
+        float scale, void* stream) {
+    if (T <= 0) return 0;
+    if (R < 1 || R > LAT_MAX_ACC * LAT_THREADS || D < R || H < 1 || page_size < 1) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(T, H);
+    const size_t smem = (size_t)(D + LAT_THREADS + 33) * sizeof(float);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(latent_attention_general_kernel<bf16>, grid, dim3(LAT_THREADS), smem, s, 1,
+                         (const bf16*)qa, (bf16*)out, (const bf16*)cache, block_table, max_blocks, req_of_token,
+                         positions, H, R, D, page_size, window, scale);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(latent_attention_general_kernel<float>, grid, dim3(LAT_THREADS), smem, s, 1,
+                         (const float*)qa, (float*)out, (const float*)cache, block_table, max_blocks, req_of_token,
+                         positions, H, R, D, page_size, window, scale);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -122,6 +122,75 @@ extern "C" int rg_add_rmsnorm(float* resid, const void* pending, int pending_dty
     return RG_ERR_UNSUPPORTED;
 }
 
+// The residual step of a block with a norm behind each part as well as before it:
+//   u = post_w * y / sqrt(mean(y^2) + post_eps)    the part's output y, normed (post_w holds the norm's weight
+//                                                  with whatever constant factors follow it multiplied in)
+//   r = residual[row] + u                          32-bit, written back
+//   out = w * r / sqrt(mean(r^2) + eps)            the next part's input; with w == nullptr out = r, unnormed
+//                                                  (a copy of the stream in the activation type); out == nullptr: none
+// Both sums of squares, both roots and the additions are 32-bit; y is read twice (the second read hits L1/L2).
+// post_w == nullptr adds y as it is.  `rows` as in add_rmsnorm_kernel.  out rows are out_ld elements apart.
+template <typename P, typename O>
+__global__ void add_postnorm_rmsnorm_kernel(float* __restrict__ resid, const P* __restrict__ pending,
+                                            const float* __restrict__ post_w, float post_eps,
+                                            const float* __restrict__ w, float eps, O* __restrict__ out, int out_ld,
+                                            const int* __restrict__ rows, int H) {
+    __shared__ float scratch[33];
+    pdl_wait();
+    pdl_trigger();
+    const int orow = blockIdx.x;
+    const int srow = rows ? rows[orow] : orow;
+    float* r = resid + (size_t)srow * H;
+    const P* p = pending ? pending + (size_t)srow * H : nullptr;
+    float inv_y = 1.f;
+    if (p && post_w) {
+        float sy = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) { const float y = to_f32(p[i]); sy += y * y; }
+        sy = block_sum(sy, scratch);
+        inv_y = rsqrtf(sy / (float)H + post_eps);
+    }
+    const bool write_back = (rows == nullptr) && (p != nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (p) v += post_w ? to_f32(p[i]) * inv_y * post_w[i] : to_f32(p[i]);
+        if (write_back) r[i] = v;
+        ss += v * v;
+    }
+    if (out == nullptr) return;
+    float inv = 1.f;
+    if (w) {
+        ss = block_sum(ss, scratch);
+        inv = rsqrtf(ss / (float)H + eps);
+    } else {
+        __syncthreads();
+    }
+    O* o = out + (size_t)orow * out_ld;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = r[i];
+        if (p && !write_back) v += post_w ? to_f32(p[i]) * inv_y * post_w[i] : to_f32(p[i]);
+        o[i] = from_f32<O>(w ? v * inv * w[i] : v);
+    }
+}
+
+extern "C" int rg_add_postnorm_rmsnorm(float* resid, const void* pending, int pending_dtype, const float* post_w,
+                                       float post_eps, const float* w, float eps, void* out, int out_dtype,
+                                       int out_ld, const int* rows, int n_out_rows, int H, void* stream) {
+    if (n_out_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+#define RG_PNORM(P, O) return rg_launch(add_postnorm_rmsnorm_kernel<P, O>, dim3(n_out_rows), dim3(threads), 0, s, 1, \
+        resid, (const P*)pending, post_w, post_eps, w, eps, (O*)out, out_ld, rows, H)
+    if (pending == nullptr) pending_dtype = RG_DTYPE_F32;
+    if (out == nullptr) out_dtype = RG_DTYPE_F32;
+    if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_BF16) RG_PNORM(bf16, bf16);
+    if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_F32) RG_PNORM(float, float);
+    if (pending_dtype == RG_DTYPE_F32 && out_dtype == RG_DTYPE_BF16) RG_PNORM(float, bf16);
+    if (pending_dtype == RG_DTYPE_BF16 && out_dtype == RG_DTYPE_F32) RG_PNORM(bf16, float);
+#undef RG_PNORM
+    return RG_ERR_UNSUPPORTED;
+}
+
 extern "C" int rg_residual_add(float* resid, const void* pending, int pending_dtype, long long n, void* stream) {
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;

@@ -134,6 +134,218 @@ def add_rmsnorm(resid: torch.Tensor, pending, weight: torch.Tensor, eps: float, 
     return out
 
 
+
+class PendingNormed:
+    """A part's output that is still to be RMS-normed (``weight``, ``eps``; the
+    weight holds whatever constant factors follow the norm) before it is added
+    to the residual: a norm that follows does both inside its own kernel;
+    ``materialize()`` computes the normed rows in 32-bit."""
+
+    __slots__ = ("y", "weight", "eps")
+
+    def __init__(self, y, weight, eps: float):
+        self.y, self.weight, self.eps = y, weight, float(eps)
+
+    @property
+    def shape(self):
+        return self.y.shape
+
+    def materialize(self) -> torch.Tensor:
+        out = torch.zeros(self.y.shape, dtype=torch.float32, device=self.y.device)
+        add_postnorm_rmsnorm(out, self, None, 0.0, None)
+        return out
+
+
+def add_postnorm_rmsnorm(resid: torch.Tensor, pending, weight, eps: float, out_dtype, rows: torch.Tensor | None = None,
+                         out: torch.Tensor | None = None):
+    """resid += post-norm of ``pending`` (a ``PendingNormed``; a plain tensor is
+    added as it is; None adds nothing), in place and in 32-bit; then the
+    RMSNorm (``weight``, ``eps``) of the new rows in ``out_dtype``.  With
+    ``weight`` None and an ``out_dtype`` the rows are returned unnormed (a copy
+    of the stream in that type); with ``out_dtype`` None nothing is returned.
+    ``rows`` as in ``add_rmsnorm``.  ``out``: a [rows, H] view to write into,
+    whose rows may be further apart than H."""
+    _check(resid, "resid", torch.float32)
+    T, H = resid.shape
+    post_w, post_eps, y = None, 0.0, pending
+    if isinstance(pending, PendingNormed):
+        post_w, post_eps, y = pending.weight, pending.eps, pending.y
+        _check(post_w, "post-norm weight", torch.float32)
+        if post_w.numel() != H:
+            raise KernelError(f"post-norm weight has {post_w.numel()} elements, rows have {H}")
+    if y is not None:
+        _check(y, "pending")
+        if y.shape != resid.shape:
+            raise KernelError(f"pending {tuple(y.shape)} vs residual {tuple(resid.shape)}")
+    if weight is not None:
+        _check(weight, "weight", torch.float32)
+        if weight.numel() != H:
+            raise KernelError(f"norm weight has {weight.numel()} elements, rows have {H}")
+    n_out = T
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+        n_out = rows.numel()
+    if out is None and out_dtype is not None:
+        out = torch.empty((n_out, H), dtype=out_dtype, device=resid.device)
+    if out is not None:
+        if (not out.is_cuda or out.dim() != 2 or out.shape != (n_out, H) or out.stride(1) != 1
+                or out.stride(0) < H):
+            raise KernelError(f"out must be a CUDA [rows, {H}] view with unit column stride")
+    _ok(_fn("norm", "rg_add_postnorm_rmsnorm")(
+        _ptr(resid), _ptr(y), c_int(_dtype_code(y) if y is not None else 0), _ptr(post_w), c_float(post_eps),
+        _ptr(weight), c_float(eps), _ptr(out), c_int(_dtype_code(out) if out is not None else 0),
+        c_int(out.stride(0) if out is not None else H), _ptr(rows), c_int(n_out), c_int(H), _stream()),
+        "add_postnorm_rmsnorm")
+    return out
+
+
+def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
+    """logits <- cap * tanh(logits / cap), in place (32-bit)."""
+    _check(logits, "logits", torch.float32)
+    if not cap > 0.0:
+        raise KernelError(f"a soft cap must be positive, got {cap}")
+    _ok(_fn("activation", "rg_softcap")(_ptr(logits), c_float(cap), c_longlong(logits.numel()), _stream()), "softcap")
+    return logits
+
+
+def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa: torch.Tensor, cache, norm_w: torch.Tensor, eps: float,
+                      freq: torch.Tensor, rot_dims: int, positions: torch.Tensor, slots, H: int, dn: int, dr: int,
+                      R: int) -> None:
+    """Per token of ``proj`` [T, H (dn + dr) + R + dr] (queries per head as
+    [dn plain | dr rotated], then at ``kv_off`` the compressed key/value vector
+    [R | dr]): rotate every head's rotated part into ``qa`` [T, H, R + dr][:, :, R:],
+    and write [RMS norm of the R latent numbers times ``norm_w`` | rotated key
+    part] into row ``slots[t]`` of ``cache`` [pages, page, R + dr] (``slots``
+    None or a negative slot: no write).  Rotation: pairs (i, i + rot_dims / 2) by
+    position * ``freq[i]``, in 32-bit."""
+    _check(proj, "proj")
+    _check(qa, "qa", proj.dtype)
+    _check(norm_w, "norm_w", torch.float32)
+    _check(freq, "freq", torch.float32)
+    _check(positions, "positions", torch.int32)
+    T = proj.shape[0]
+    D = R + dr
+    if proj.shape[1] < kv_off + D or kv_off < H * (dn + dr) or qa.shape != (T, H, D) or positions.numel() != T:
+        raise KernelError(f"latent_rope_cache: proj {tuple(proj.shape)}, qa {tuple(qa.shape)} do not match "
+                          f"{H} heads x ({dn} + {dr}), latent {R}")
+    if norm_w.numel() != R or freq.numel() < rot_dims // 2:
+        raise KernelError("latent_rope_cache: norm weight or frequency table of the wrong size")
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        _check(cache, "cache", proj.dtype)
+        if cache.shape[-1] != D:
+            raise KernelError(f"latent cache rows hold {cache.shape[-1]} numbers, the mixer writes {D}")
+    _ok(_fn("attention_latent", "rg_latent_rope_cache")(
+        _ptr(proj), c_int(proj.stride(0)), c_int(kv_off), _ptr(qa), _ptr(cache if slots is not None else None),
+        c_int(_dtype_code(proj)), _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions),
+        _ptr(slots), c_int(T), c_int(H), c_int(dn), c_int(dr), c_int(R), _stream()), "latent_rope_cache")
+
+
+def latent_attention_general(qa: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                             req_of_token: torch.Tensor, positions: torch.Tensor, R: int, window: int,
+                             scale: float) -> torch.Tensor:
+    """Attention of ``qa`` [T, H, D] over the latent cache [pages, page, D]: the
+    scores use all D numbers of a cache row, the values are its first R.
+    Returns [T, H, R].  32-bit arithmetic, any sizes with R <= 1024."""
+    _check(qa, "qa")
+    _check(cache, "cache", qa.dtype)
+    _check(block_table, "block_table", torch.int32)
+    _check(req_of_token, "req_of_token", torch.int32)
+    _check(positions, "positions", torch.int32)
+    T, H, D = qa.shape
+    if cache.dim() != 3 or cache.shape[2] != D or R > D:
+        raise KernelError(f"latent cache {tuple(cache.shape)} does not match queries of {D} numbers, latent {R}")
+    out = torch.empty((T, H, R), dtype=qa.dtype, device=qa.device)
+    _ok(_fn("attention_latent", "rg_latent_attention_general")(
+        _ptr(qa), _ptr(out), _ptr(cache), c_int(_dtype_code(qa)), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(req_of_token), _ptr(positions), c_int(T), c_int(H), c_int(R), c_int(D), c_int(cache.shape[1]),
+        c_int(window or 0), c_float(scale), _stream()), "latent_attention_general")
+    return out
+
+
+MOE_TILE_ROWS = 32
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int):
+    """Router of a mixture of experts: softmax of the 32-bit logits ``router`` x
+    over all N outputs; the ``top`` outputs with the largest score + correction;
+    weights = their scores over their sum.  Returns (ids int32 [T, top],
+    weights float32 [T, top])."""
+    _check(x, "x")
+    _check(router, "router", torch.float32)
+    _check(correction, "correction", torch.float32)
+    T, W = x.shape
+    N = router.shape[0]
+    if router.shape[1] != W or correction.numel() != N:
+        raise KernelError(f"router {tuple(router.shape)}, correction {correction.numel()} vs rows of {W}")
+    ids = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    _ok(_fn("moe", "rg_moe_route")(_ptr(x), c_int(_dtype_code(x)), _ptr(router), _ptr(correction), _ptr(ids),
+                                   _ptr(weights), c_int(T), c_int(W), c_int(N), c_int(top), _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_align(ids: torch.Tensor, num_experts: int, tile_rows: int = MOE_TILE_ROWS):
+    """Group the (token, choice) pairs of ``ids`` [T, top] by expert (outputs
+    from ``num_experts`` on have no expert behind them and get no place).
+    Returns (sorted_pair [P], pair_pos [P] (-1: no place), tiles [max_tiles, 3]
+    = (expert or -1, first place, places))."""
+    _check(ids, "ids", torch.int32)
+    P = ids.numel()
+    max_tiles = (P + tile_rows - 1) // tile_rows + num_experts
+    sorted_pair = torch.empty(P, dtype=torch.int32, device=ids.device)
+    pair_pos = torch.empty(P, dtype=torch.int32, device=ids.device)
+    tiles = torch.empty((max_tiles, 3), dtype=torch.int32, device=ids.device)
+    _ok(_fn("moe", "rg_moe_align")(_ptr(ids), c_int(P), c_int(num_experts), c_int(tile_rows), _ptr(sorted_pair),
+                                   _ptr(pair_pos), _ptr(tiles), c_int(max_tiles), _stream()), "moe_align")
+    return sorted_pair, pair_pos, tiles
+
+
+def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles: torch.Tensor, places: int,
+                     gated: bool, tile_rows: int = MOE_TILE_ROWS) -> torch.Tensor:
+    """out[pos] = W_e a_row(pos) for every place of the tile list, e the tile's
+    expert; ``w`` [E, N, K] (``gated``: [E, 2 N, K] = gate rows then up rows and
+    out = silu(gate) * up).  Row ``pos`` of the input is ``a[src[pos] // src_div]``
+    or, without ``src``, ``a[pos]``.  Returns [places, N]; rows that belong to no
+    tile are not written."""
+    _check(a, "a")
+    _check(w, "w", a.dtype)
+    _check(tiles, "tiles", torch.int32)
+    if src is not None:
+        _check(src, "src", torch.int32)
+    E, rows_w, K = w.shape
+    N = rows_w // 2 if gated else rows_w
+    if a.shape[1] != K or (gated and rows_w % 2):
+        raise KernelError(f"moe_grouped_gemm: a {tuple(a.shape)} vs w {tuple(w.shape)}")
+    out = torch.empty((places, N), dtype=a.dtype, device=a.device)
+    _ok(_fn("moe", "rg_moe_grouped_gemm")(
+        _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), c_int(_dtype_code(a)),
+        _ptr(tiles), c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0), _stream()),
+        "moe_grouped_gemm")
+    return out
+
+
+def moe_combine(x: torch.Tensor, y, shared, ids: torch.Tensor, weights: torch.Tensor, pair_pos: torch.Tensor,
+                num_experts: int) -> torch.Tensor:
+    """float32 [T, W] = sum over a token's choices of weight * (the expert's
+    row of ``y``, or the token's own row of ``x`` for a choice with no expert
+    behind it), plus ``shared`` if given."""
+    _check(x, "x")
+    T, W = x.shape
+    top = ids.shape[1]
+    if y is not None:
+        _check(y, "y", x.dtype)
+    if shared is not None:
+        _check(shared, "shared", x.dtype)
+        if shared.shape != x.shape:
+            raise KernelError(f"shared {tuple(shared.shape)} vs x {tuple(x.shape)}")
+    out = torch.empty((T, W), dtype=torch.float32, device=x.device)
+    _ok(_fn("moe", "rg_moe_combine")(_ptr(x), _ptr(y), _ptr(shared), c_int(_dtype_code(x)), _ptr(ids), _ptr(weights),
+                                     _ptr(pair_pos), _ptr(out), c_int(T), c_int(W), c_int(num_experts), c_int(top),
+                                     _stream()), "moe_combine")
+    return out
+
+
 def residual_add(resid: torch.Tensor, pending: torch.Tensor) -> None:
     _check(resid, "resid", torch.float32)
     _check(pending, "pending")

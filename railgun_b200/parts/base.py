@@ -41,6 +41,9 @@ class Norm(Part):
     both away from parts that did not ask for them."""
 
     fuses_pending_linear = False
+    # True for a norm whose ``add_norm`` also takes ``pending`` as an ``ops.PendingNormed`` (a part's output that
+    # another norm is still to be applied to before the addition) and does both norms in one pass.
+    fuses_post_norm = False
 
     def add_norm(self, resid, pending, rows=None):
         raise NotImplementedError
@@ -71,6 +74,8 @@ def normed_input(norm, part, stream, rows=None):
     part that both declare that they take them."""
     pending = stream.pending
     if isinstance(pending, ops.PendingLinear) and not getattr(norm, "fuses_pending_linear", False):
+        pending = pending.materialize()
+    if isinstance(pending, ops.PendingNormed) and not getattr(norm, "fuses_post_norm", False):
         pending = pending.materialize()
     h = norm.add_norm(stream.resid, pending) if rows is None else norm.add_norm(stream.resid, pending, rows=rows)
     if isinstance(h, ops.NormedRows) and not getattr(part, "takes_normed_rows", False):
@@ -142,11 +147,27 @@ class Stream:
     """The residual stream during a step: the 32-bit sum and the last part's
     output, not yet added (it is added inside the next norm's kernel)."""
 
-    __slots__ = ("resid", "pending")
+    __slots__ = ("resid", "pending", "kept")
 
     def __init__(self, resid):
         self.resid = resid
         self.pending = None
+        self.kept = {}              # what stream operations keep from the start of the step, by operation
+
+
+class StreamOp(Part):
+    """An operation on the whole residual stream between layers (a schedule
+    entry's ``before``).  ``begin(stream, batch)`` runs once per step right
+    after the embedding (the stream then is the embedding's output) and may
+    keep something in ``stream.kept[self]``; ``apply(stream, batch)`` runs where
+    the schedule names the operation and leaves the new stream in
+    ``stream.resid`` with nothing pending."""
+
+    def begin(self, stream, batch):
+        pass
+
+    def apply(self, stream, batch):
+        raise NotImplementedError
 
 
 class Arrangement:

@@ -6,11 +6,25 @@ usual block is x = x + mixer(norm(x)); x = x + ffn(norm(x))
 inside the next norm's kernel, in 32-bit; at small decode batches the
 addition moves into the kernel of the product before it and the norm into the
 kernel of the product after it (ops.PendingLinear, ops.NormedRows).
+
+"sandwich": a norm behind each part as well as before it,
+x = x + post_norm(part(norm(x))); constant factors on the branch (a residual
+multiplier, a per-feature layer scale) are part of the post-norm's weight.
+The post-norm, the 32-bit addition and the next branch's norm are one kernel
+(ops.PendingNormed).
+
+"reinject" (a stream operation): x <- W [x; x0] with x0 the embedding's
+output, for models that feed the input again at the start of a pass over a
+span of layers.
 """
 from __future__ import annotations
 
-from .base import Arrangement, normed_input
-from .registry import register_arrangement
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import Arrangement, StreamOp, normed_input
+from .registry import register_arrangement, register_stream_op
 
 
 class PreNorm(Arrangement):
@@ -24,4 +38,43 @@ class PreNorm(Arrangement):
                 stream.pending = b.part.forward(h, batch, **more)
 
 
+class Sandwich(Arrangement):
+    def run(self, layer, stream, batch, cache, writes):
+        for b in layer.branches:
+            if b.post_norm is None:
+                raise ValueError("the 'sandwich' arrangement needs a post_norm on every branch")
+            h = normed_input(b.norm, b.part, stream)
+            y = b.part.forward(h, batch, cache, writes) if b.role == "mixer" else b.part.forward(h, batch)
+            stream.pending = ops.PendingNormed(y, b.post_norm.weight, b.post_norm.eps)
+
+
+class Reinject(StreamOp):
+    """params: ``hidden_size``, ``name`` (the matrix [H, 2 H], the stream's half first)."""
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        return {p["name"]: TensorSpec((p["hidden_size"], 2 * p["hidden_size"]))}
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        self.H = p["hidden_size"]
+        self.weight = tensors.get(p["name"], env.dtype)
+
+    def begin(self, stream, batch):
+        # [x | x0] in the activation type: the right half is filled here, once per step
+        both = torch.empty((stream.resid.shape[0], 2 * self.H), dtype=self.env.dtype, device=stream.resid.device)
+        ops.add_postnorm_rmsnorm(stream.resid, None, None, 0.0, None, out=both[:, self.H:])
+        stream.kept[self] = both
+
+    def apply(self, stream, batch):
+        both = stream.kept[self]
+        # what is pending is added (32-bit), the sum goes into the left half, the product is the new stream
+        pending = stream.pending.materialize() if isinstance(stream.pending, ops.PendingLinear) else stream.pending
+        ops.add_postnorm_rmsnorm(stream.resid, pending, None, 0.0, None, out=both[:, :self.H])
+        stream.pending = None
+        stream.resid = ops.linear(both, self.weight, out_dtype=torch.float32)
+
+
 register_arrangement("prenorm", PreNorm)
+register_arrangement("sandwich", Sandwich)
+register_stream_op("reinject", Reinject)

@@ -33,7 +33,8 @@ class TokenEmbedding(Embedding):
 
 class LMHead(Head):
     """params: ``vocab_size``, ``hidden_size``, ``name`` (full tensor name; the
-    embedding's name when tied, so both share one tensor)."""
+    embedding's name when tied, so both share one tensor); optional
+    ``softcap`` c: logits <- c tanh(logits / c)."""
 
     @classmethod
     def tensor_specs(cls, p, prefix):
@@ -42,9 +43,11 @@ class LMHead(Head):
     def __init__(self, p, prefix, env, tensors):
         super().__init__(p, prefix, env, tensors)
         self.weight = tensors.get(p["name"], env.dtype)
+        self.softcap = float(p["softcap"]) if p.get("softcap") else None
 
     def logits(self, h):
-        return ops.linear(h, self.weight, out_dtype=torch.float32)
+        z = ops.linear(h, self.weight, out_dtype=torch.float32)
+        return ops.softcap_(z, self.softcap) if self.softcap else z
 
 
 register_embedding("token_embedding", TokenEmbedding)

@@ -1,0 +1,111 @@
+"""Attention with a compressed key/value cache shared by all heads.
+
+Per token the mixer keeps one vector c of ``kv_rank`` numbers (a
+down-projection of its input, RMS-normed) and one rotated key part of
+``rot_dim`` numbers; head h's keys and values are U_k[h] c and U_v[h] c.  A
+head's score is scale * (q_plain . U_k[h] c + q_rot . k_rot), so with the
+plain query part taken through U_k[h]^T once, every head reads the same
+cache rows: scores over [c | k_rot], values = c, and the head's output is
+U_v[h] applied to the weighted sum of c.  Nothing is ever expanded per head.
+
+  proj          one product for the queries and the down-projection
+  qa[:, h, :R]  = U_k[h]^T q_plain[h]          batched product (library)
+  qa[:, h, R:]  = rotate(q_rot[h]);  cache row = [rmsnorm(c) | rotate(k_rot)]   (one kernel)
+  o_lat         attention over the cache                                        (kernels)
+  out           = W_o concat_h(U_v[h] o_lat[h])    batched product, product
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.manager import PagedKVNeed
+from ..weights.loader import TensorSpec
+from .base import Mixer
+from .registry import register_mixer
+
+
+def rotary_frequencies(dims: int, base: float) -> torch.Tensor:
+    """f_i = base^(-2i/dims), i < dims/2: computed in 64-bit, stored in 32-bit."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    return (float(base) ** (-2.0 * i / dims)).to(torch.float32)
+
+
+class LatentAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``head_dim`` (unrotated query/key
+    numbers per head), ``rot_dim`` (rotated ones), ``v_dim``, ``kv_rank``,
+    ``scale``, ``rot_dims`` (how many of the rotated part's numbers are rotated,
+    in pairs (i, i + rot_dims/2)), ``rot_base``, ``eps`` (of the latent's norm),
+    ``window`` (0: none), ``names`` (optional: tensor names after the prefix for
+    q, dkv, dkv_norm, uk, uv, o)."""
+
+    NAMES = dict(q="mix.q", dkv="mix.dkv", dkv_norm="mix.dkv.norm", uk="mix.uk", uv="mix.uv", o="mix.o")
+
+    @classmethod
+    def _names(cls, p, prefix):
+        return {k: prefix + v for k, v in {**cls.NAMES, **(p.get("names") or {})}.items()}
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        W, H, dn, dr, dv, R = (p["hidden_size"], p["num_heads"], p["head_dim"], p["rot_dim"], p["v_dim"],
+                               p["kv_rank"])
+        n = cls._names(p, prefix)
+        return {
+            n["q"]: TensorSpec((H * (dn + dr), W)),
+            n["dkv"]: TensorSpec((R + dr, W)),
+            n["dkv_norm"]: TensorSpec((R,), init="norm"),
+            n["uk"]: TensorSpec((H * dn, R)),
+            n["uv"]: TensorSpec((H * dv, R)),
+            n["o"]: TensorSpec((W, H * dv)),
+        }
+
+    @classmethod
+    def cache_need(cls, p):
+        D = p["kv_rank"] + p["rot_dim"]
+        return PagedKVNeed(1, D, int(p.get("window") or 0), page_shape=("page", D))
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        self.H, self.dn, self.dr, self.dv, self.R = (p["num_heads"], p["head_dim"], p["rot_dim"], p["v_dim"],
+                                                     p["kv_rank"])
+        self.D = self.R + self.dr
+        self.rot_dims = int(p["rot_dims"])
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.dr:
+            raise ValueError(f"{self.rot_dims} rotated numbers do not fit a rotated part of {self.dr}")
+        if self.R > 1024:
+            raise ValueError(f"a latent of {self.R} numbers is above the attention kernels' limit of 1024")
+        self.window = int(p.get("window") or 0)
+        self.scale = float(p["scale"])
+        self.eps = float(p["eps"])
+        n = self._names(p, prefix)
+        self.w_proj = torch.cat([tensors.get(n["q"], env.dtype), tensors.get(n["dkv"], env.dtype)], dim=0).contiguous()
+        tensors.drop(n["q"], n["dkv"])
+        self.kv_off = self.H * (self.dn + self.dr)
+        self.norm_w = tensors.get(n["dkv_norm"], torch.float32)
+        self.w_uk = tensors.get(n["uk"], env.dtype).view(self.H, self.dn, self.R)                      # [H, dn, R]
+        self.w_uv_t = tensors.get(n["uv"], env.dtype).view(self.H, self.dv, self.R).transpose(1, 2)    # [H, R, dv]
+        self.w_o = tensors.get(n["o"], env.dtype)
+        self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, float(p["rot_base"])),
+                                        lambda: rotary_frequencies(self.rot_dims, p["rot_base"]).to(env.device))
+
+    def forward(self, x, batch, cache, writes=True):
+        H, dn, dr, dv, R, D = self.H, self.dn, self.dr, self.dv, self.R, self.D
+        T = x.shape[0]
+        proj = ops.linear(x, self.w_proj)                                                  # [T, H (dn + dr) + R + dr]
+        qa = torch.empty((T, H, D), dtype=proj.dtype, device=proj.device)
+        q_plain = proj[:, :self.kv_off].view(T, H, dn + dr)[:, :, :dn].transpose(0, 1)     # [H, T, dn], no copy
+        torch.bmm(q_plain, self.w_uk, out=qa[:, :, :R].transpose(0, 1))
+        ops.latent_rope_cache(proj, self.kv_off, qa, cache.kv, self.norm_w, self.eps, self.freq, self.rot_dims,
+                              batch.positions, batch.slot_mapping[cache.group] if writes else None, H, dn, dr, R)
+        o_lat = self.attend(qa, batch, cache)                                              # [T, H, R]
+        heads = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
+        torch.bmm(o_lat.transpose(0, 1), self.w_uv_t, out=heads.view(T, H, dv).transpose(0, 1))
+        return ops.linear(heads, self.w_o)
+
+    def attend(self, qa, batch, cache):
+        table = batch.block_table[cache.group]
+        return ops.latent_attention_general(qa, cache.kv, table, batch.req_of_token, batch.positions, self.R,
+                                            self.window, self.scale)
+
+
+register_mixer("latent_attention", LatentAttention)

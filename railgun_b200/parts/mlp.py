@@ -13,28 +13,28 @@ from .registry import register_feed_forward
 
 
 class SwiGLU(FeedForward):
-    """params: ``hidden_size``, ``intermediate_size``."""
+    """params: ``hidden_size``, ``intermediate_size``; optional ``names`` (the
+    gate, up and down matrices' names after the prefix)."""
+
+    NAMES = ("mlp.gate_proj.weight", "mlp.up_proj.weight", "mlp.down_proj.weight")
 
     @classmethod
     def tensor_specs(cls, p, prefix):
         H, I = p["hidden_size"], p["intermediate_size"]
-        return {
-            prefix + "mlp.gate_proj.weight": TensorSpec((I, H)),
-            prefix + "mlp.up_proj.weight": TensorSpec((I, H)),
-            prefix + "mlp.down_proj.weight": TensorSpec((H, I)),
-        }
+        gate, up, down = p.get("names") or cls.NAMES
+        return {prefix + gate: TensorSpec((I, H)), prefix + up: TensorSpec((I, H)), prefix + down: TensorSpec((H, I))}
 
     def __init__(self, p, prefix, env, tensors):
         super().__init__(p, prefix, env, tensors)
-        m = prefix + "mlp."
-        gate, up = tensors.get(m + "gate_proj.weight", env.dtype), tensors.get(m + "up_proj.weight", env.dtype)
+        n_gate, n_up, n_down = (prefix + n for n in (p.get("names") or self.NAMES))
+        gate, up = tensors.get(n_gate, env.dtype), tensors.get(n_up, env.dtype)
         # bfloat16 with I % 8 == 0: gate and up rows interleaved in blocks of 8, which lets the decode
         # product apply SiLU-mul in its epilogue; otherwise gate rows, then up rows
         self.interleaved = env.dtype == torch.bfloat16 and p["intermediate_size"] % 8 == 0
         self.w_gate_up = (ops.interleave_gate_up(gate, up) if self.interleaved
                           else torch.cat([gate, up], dim=0).contiguous())
-        tensors.drop(m + "gate_proj.weight", m + "up_proj.weight")
-        self.w_down = tensors.get(m + "down_proj.weight", env.dtype)
+        tensors.drop(n_gate, n_up)
+        self.w_down = tensors.get(n_down, env.dtype)
 
     takes_normed_rows = True
     defers_output = True

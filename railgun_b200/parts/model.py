@@ -12,11 +12,12 @@ from dataclasses import dataclass
 import torch
 
 from .base import CacheView, Stream, normed_input
-from .registry import ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS
+from .registry import ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, STREAM_OPS
 from .spec import BuildEnv, ModelSpec
 # importing the modules registers the built-in parts
 from . import attention as _attention, block as _block, embedding as _embedding  # noqa: F401
 from . import mlp as _mlp, norm as _norm, rope as _rope  # noqa: F401
+from . import latent_attention as _latent_attention, moe as _moe  # noqa: F401
 
 
 def _part_registry(role: str):
@@ -30,7 +31,11 @@ def expected_tensors(spec: ModelSpec) -> dict:
     for layer in spec.layers:
         for b in layer.branches():
             out.update(NORMS.get(b.norm.kind).tensor_specs(b.norm.params, layer.prefix))
+            if b.post_norm is not None:
+                out.update(NORMS.get(b.post_norm.kind).tensor_specs(b.post_norm.params, layer.prefix))
             out.update(_part_registry(b.role).get(b.part.kind).tensor_specs(b.part.params, layer.prefix))
+    for op in spec.stream_ops:
+        out.update(STREAM_OPS.get(op.kind).tensor_specs(op.params, ""))
     out.update(NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm.params, ""))
     out.update(HEADS.get(spec.head.kind).tensor_specs(spec.head.params, ""))
     return out
@@ -74,6 +79,7 @@ class Branch:
     norm: object
     part: object
     role: str                       # "mixer" or "ffn"
+    post_norm: object = None
 
 
 @dataclass
@@ -105,14 +111,19 @@ class DecoderModel:
             self.layers.append(Layer(
                 branches=[Branch(NORMS.get(b.norm.kind)(b.norm.params, ls.prefix, env, tensors),
                                  _part_registry(b.role).get(b.part.kind)(b.part.params, ls.prefix, env, tensors),
-                                 b.role) for b in ls.branches()],
+                                 b.role,
+                                 NORMS.get(b.post_norm.kind)(b.post_norm.params, ls.prefix, env, tensors)
+                                 if b.post_norm is not None else None) for b in ls.branches()],
                 arrangement=ARRANGEMENTS.get(ls.arrangement)(),
             ))
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, "", env, tensors)
         self.head = HEADS.get(spec.head.kind)(spec.head.params, "", env, tensors)
+        self.stream_ops = [STREAM_OPS.get(op.kind)(op.params, "", env, tensors) for op in spec.stream_ops]
         self.order = spec.run_order()
         seen_writer = set()
         for e in self.order:
+            if not -1 <= e.before < len(self.stream_ops):
+                raise ValueError(f"schedule names stream operation {e.before}; the model has {len(self.stream_ops)}")
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule names layer {e.layer}; the model has {len(self.layers)}")
             if e.writes:
@@ -132,6 +143,9 @@ class DecoderModel:
             for b in layer.branches:
                 yield b.norm
                 yield b.part
+                if b.post_norm is not None:
+                    yield b.post_norm
+        yield from self.stream_ops
         yield self.final_norm
         yield self.head
 
@@ -166,7 +180,11 @@ class DecoderModel:
     def forward(self, batch, cache):
         """Run the step's tokens; return float32 logits [wanted rows, vocab] or None."""
         stream = Stream(self.embedding.embed(batch.token_ids))
+        for op in self.stream_ops:
+            op.begin(stream, batch)
         for e in self.order:
+            if e.before >= 0:
+                self.stream_ops[e.before].apply(stream, batch)
             layer = self.layers[e.layer]
             layer.arrangement.run(layer, stream, batch, cache.view(e.cache), e.writes)
         if batch.num_wanted == 0:

@@ -1,0 +1,84 @@
+"""A mixture of gated experts with a softmax router.
+
+Router logits are 32-bit; scores are their softmax over all router outputs;
+the ``top`` outputs with the largest score + correction are chosen, and their
+weights are the scores themselves over their sum.  The first ``experts``
+outputs stand for gated feed-forwards down(silu(gate h) * (up h)), the
+``identity`` outputs after them for experts that return their input.  An
+optional shared expert of the same form runs for every token and is added.
+
+The experts' matrices are stacked at load ([E, 2F, W] gate rows then up rows,
+[E, W, F]); the step groups its (token, choice) pairs by expert on the device
+and runs both products over the groups, so nothing is read back to the host
+and the step stays capturable.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..weights.loader import TensorSpec
+from .base import FeedForward
+from .mlp import SwiGLU
+from .registry import register_feed_forward
+
+
+class RoutedExperts(FeedForward):
+    """params: ``hidden_size``, ``experts``, ``identity``, ``top``,
+    ``expert_size`` (an expert's inner size), ``shared_size`` (the shared
+    expert's, or None), ``base`` (tensor names after the prefix start with it:
+    ``<base>e<i>.gate|up|down``, ``<base>router``, ``<base>correction``,
+    ``<base>shared.gate|up|down``)."""
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        W, E, N, F = p["hidden_size"], p["experts"], p["experts"] + p["identity"], p["expert_size"]
+        b = prefix + p.get("base", "mlp.")
+        out = {b + "router": TensorSpec((N, W)), b + "correction": TensorSpec((N,), init="zeros")}
+        for e in range(E):
+            out[f"{b}e{e}.gate"] = TensorSpec((F, W))
+            out[f"{b}e{e}.up"] = TensorSpec((F, W))
+            out[f"{b}e{e}.down"] = TensorSpec((W, F))
+        if p.get("shared_size"):
+            out.update(SwiGLU.tensor_specs(cls._shared_params(p), prefix))
+        return out
+
+    @staticmethod
+    def _shared_params(p):
+        b = p.get("base", "mlp.")
+        return dict(hidden_size=p["hidden_size"], intermediate_size=p["shared_size"],
+                    names=(b + "shared.gate", b + "shared.up", b + "shared.down"))
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        self.E, self.top = int(p["experts"]), int(p["top"])
+        self.N = self.E + int(p["identity"])
+        if not 1 <= self.top <= self.N:
+            raise ValueError(f"{self.top} choices among {self.N} router outputs")
+        b = prefix + p.get("base", "mlp.")
+        self.router = tensors.get(b + "router", torch.float32)
+        self.correction = tensors.get(b + "correction", torch.float32)
+        if self.E:
+            self.w_gate_up = torch.stack([torch.cat([tensors.get(f"{b}e{e}.gate", env.dtype),
+                                                     tensors.get(f"{b}e{e}.up", env.dtype)], dim=0)
+                                          for e in range(self.E)]).contiguous()                    # [E, 2F, W]
+            self.w_down = torch.stack([tensors.get(f"{b}e{e}.down", env.dtype) for e in range(self.E)]).contiguous()
+            tensors.drop(*[f"{b}e{e}.{n}" for e in range(self.E) for n in ("gate", "up", "down")])
+        self.shared = SwiGLU(self._shared_params(p), prefix, env, tensors) if p.get("shared_size") else None
+
+    def forward(self, x, batch):
+        T = x.shape[0]
+        ids, weights = ops.moe_route(x, self.router, self.correction, self.top)
+        y = pair_pos = None
+        if self.E:
+            sorted_pair, pair_pos, tiles = ops.moe_align(ids, self.E)
+            places = T * self.top
+            act = ops.moe_grouped_gemm(x, sorted_pair, self.top, self.w_gate_up, tiles, places, gated=True)
+            y = ops.moe_grouped_gemm(act, None, 1, self.w_down, tiles, places, gated=False)
+        else:
+            pair_pos = ids
+        shared = self.shared.forward(x, batch) if self.shared is not None else None
+        return ops.moe_combine(x, y, shared, ids, weights, pair_pos, self.E)
+
+
+register_feed_forward("routed_experts", RoutedExperts)

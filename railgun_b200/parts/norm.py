@@ -16,20 +16,34 @@ from .registry import register_norm
 
 
 class RMSNorm(Norm):
-    """params: ``size``, ``eps``, ``name`` (weight tensor name after the prefix)."""
+    """params: ``size``, ``eps``, ``name`` (weight tensor name after the prefix);
+    optional ``scale_name`` (a second per-feature vector, a layer scale, that
+    multiplies the normed value) and ``mult`` (a constant that does): both are
+    multiplied into the weight at load, in 32-bit."""
 
     @classmethod
     def tensor_specs(cls, params, prefix):
-        return {prefix + params["name"]: TensorSpec((params["size"],), init="norm")}
+        out = {prefix + params["name"]: TensorSpec((params["size"],), init="norm")}
+        if params.get("scale_name"):
+            out[prefix + params["scale_name"]] = TensorSpec((params["size"],), init="norm")
+        return out
 
     def __init__(self, params, prefix, env, tensors):
         super().__init__(params, prefix, env, tensors)
         self.eps = float(params["eps"])
         self.weight = tensors.get(prefix + params["name"], torch.float32)
+        if params.get("scale_name"):
+            self.weight = self.weight * tensors.get(prefix + params["scale_name"], torch.float32)
+        if params.get("mult") is not None and float(params["mult"]) != 1.0:
+            self.weight = self.weight * float(params["mult"])
+        self.weight = self.weight.contiguous()
 
     fuses_pending_linear = True
+    fuses_post_norm = True
 
     def add_norm(self, resid, pending, rows=None):
+        if isinstance(pending, ops.PendingNormed):
+            return ops.add_postnorm_rmsnorm(resid, pending, self.weight, self.eps, self.env.dtype, rows)
         if isinstance(pending, ops.PendingLinear):
             # small decode batches: the product adds its result to the residual itself and prepares this
             # norm; the product that reads the result finishes it

@@ -40,6 +40,7 @@ POSITION_ENCODINGS = PartRegistry("position encoding")
 ARRANGEMENTS = PartRegistry("block arrangement")
 EMBEDDINGS = PartRegistry("embedding")
 HEADS = PartRegistry("head")
+STREAM_OPS = PartRegistry("stream operation")
 
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
@@ -48,3 +49,4 @@ register_position_encoding = POSITION_ENCODINGS.register
 register_arrangement = ARRANGEMENTS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
+register_stream_op = STREAM_OPS.register

@@ -28,6 +28,7 @@ class SubLayer:
     norm: PartSpec
     part: PartSpec
     role: str                       # "mixer" or "ffn"
+    post_norm: PartSpec | None = None   # a norm on the part's output, for arrangements that have one
 
     def __post_init__(self):
         if self.role not in ("mixer", "ffn"):
@@ -73,10 +74,13 @@ class LayerSpec:
 @dataclass(frozen=True)
 class ScheduleEntry:
     """Run ``layer`` using cache ``cache``; ``writes`` False means the layer
-    only reads what another entry with the same cache id wrote."""
+    only reads what another entry with the same cache id wrote.  ``before``
+    names an entry of ``ModelSpec.stream_ops`` that transforms the residual
+    stream right before this layer runs (-1: none)."""
     layer: int
     cache: int
     writes: bool = True
+    before: int = -1
 
 
 @dataclass(frozen=True)
@@ -89,6 +93,7 @@ class ModelSpec:
     final_norm: PartSpec
     head: PartSpec
     schedule: tuple = ()
+    stream_ops: tuple = ()          # PartSpecs of operations on the residual stream between layers
 
     def run_order(self) -> tuple:
         if self.schedule:

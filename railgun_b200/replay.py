@@ -30,7 +30,7 @@ def make_parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each request rounded up to 64)")
     ap.add_argument("--block-size", type=int, default=16, help="tokens per cache page")
-    ap.add_argument("--max-requests", type=int, default=8, help="requests live at a time")
+    ap.add_argument("--max-requests", type=int, default=4, help="requests live at a time")
     ap.add_argument("--device", default="cuda:0")
     return ap
 
