@@ -34,7 +34,7 @@ class RoutedExperts(FeedForward):
     def tensor_specs(cls, p, prefix):
         W, E, N, F = p["hidden_size"], p["experts"], p["experts"] + p["identity"], p["expert_size"]
         b = prefix + p.get("base", "mlp.")
-        out = {b + "router": TensorSpec((N, W)), b + "correction": TensorSpec((N,), init="zeros")}
+        out = {b + "router": TensorSpec((N, W)), b + "correction": TensorSpec((N,))}
         for e in range(E):
             out[f"{b}e{e}.gate"] = TensorSpec((F, W))
             out[f"{b}e{e}.up"] = TensorSpec((F, W))

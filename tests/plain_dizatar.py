@@ -143,3 +143,28 @@ def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, return_layers
         trail.append(x)
     logits = softcap(rms_norm(x, t["final.norm"], eps) @ t["head"].T, cfg["logit_softcap"])
     return (logits, torch.stack(trail)) if return_layers else logits
+
+
+class PlainDizatar:
+    """The plain model over a folder with config.json and model.safetensors,
+    read with the test suite's own reader; 64-bit arithmetic on the stored
+    values."""
+
+    def __init__(self, model_dir):
+        import json
+        from pathlib import Path
+
+        from plain_llama import read_safetensors
+        model_dir = Path(model_dir)
+        self.cfg = json.loads((model_dir / "config.json").read_text())
+        self.tensors = {k: torch.from_numpy(v) for k, v in read_safetensors(model_dir / "model.safetensors").items()}
+
+    def forward(self, tokens, return_layers: bool = False):
+        out = forward(self.cfg, self.tensors, tokens, torch.float64, return_layers)
+        return (out[0].numpy(), out[1].numpy()) if return_layers else out.numpy()
+
+    def greedy(self, prompt, n: int) -> list:
+        toks = list(prompt)
+        for _ in range(n):
+            toks.append(int(self.forward(toks)[-1].argmax()))
+        return toks[len(prompt):]
