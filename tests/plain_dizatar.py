@@ -38,12 +38,13 @@ def rotate_half_pairs(v: torch.Tensor, positions: torch.Tensor, dims: int, base:
     return torch.cat([a * c - b * s, b * c + a * s, v[..., dims:]], dim=-1)
 
 
-def latent_attention(h: torch.Tensor, w: dict, p: dict, eps: float) -> torch.Tensor:
+def latent_attention(h: torch.Tensor, w: dict, p: dict, eps: float, return_weights: bool = False):
     """The mixer: queries per head, one compressed key/value vector per token
     that every head expands with its own matrices, one rotated key part shared
     by all heads, causal softmax, output projection.  ``w``: the mixer's tensors
     by short name; ``p``: its sizes (heads, dim, rot_dim, vdim, kv_rank, scale,
-    rot = {dims, base})."""
+    rot = {dims, base}).  With ``return_weights`` also the attention weights
+    [heads, query, key]."""
     T = h.shape[0]
     H, dn, dr, dv, R = p["heads"], p["dim"], p["rot_dim"], p["vdim"], p["kv_rank"]
     pos = torch.arange(T)
@@ -61,7 +62,7 @@ def latent_attention(h: torch.Tensor, w: dict, p: dict, eps: float) -> torch.Ten
     scores = scores.masked_fill(hidden, -math.inf)
     weights = torch.softmax(scores, dim=-1)
     out = torch.einsum("hij,jhd->ihd", weights, value).reshape(T, H * dv)
-    return out @ w["o"].T
+    return (out @ w["o"].T, weights) if return_weights else out @ w["o"].T
 
 
 def gated_expert(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
