@@ -1,0 +1,54 @@
+// Building blocks of the mma.sync kernels: asynchronous 16-byte copies into shared memory, ldmatrix,
+// the m16n8k16 bf16 product with 32-bit accumulators, the hardware 2^x, and packing of two floats.
+#pragma once
+#include "common.cuh"
+
+namespace rgmma {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// 16 bytes global -> shared; !valid fills the 16 bytes with zeros (the source is not read)
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const uint32_t d = smem_u32(dst);
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// D[16x8] += A[16x16] B[16x8], bf16 operands, fp32 accumulators
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x for x <= 0 (-inf -> 0): the hardware approximation (2 ulp), in 32-bit
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+// A barrier among the 64 threads of two warps that name the same `id` (1..4; 0 is __syncthreads).  The id is
+// an immediate in every branch so that the kernel reserves five barriers, not all sixteen.
+__device__ __forceinline__ void pair_barrier(int id) {
+    switch (id) {
+        case 1: asm volatile("bar.sync 1, 64;\n" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 2, 64;\n" ::: "memory"); break;
+        case 3: asm volatile("bar.sync 3, 64;\n" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 64;\n" ::: "memory"); break;
+    }
+}
+
+}  // namespace rgmma

@@ -11,79 +11,93 @@
 // the products run over a list of row tiles that `moe_align` writes (at most pairs / tile + E of them; the
 // launch covers that bound and unused tiles return at once), which keeps a step capturable in a CUDA graph.
 //
-//   moe_route          one warp per token
+//   moe_route          one block per four tokens: its warps share the router's rows, then take a token each
 //   moe_align          one block: counts per expert, segment starts, the pairs in expert order, the tile list
 //   moe_grouped_gemm   32-bit arithmetic on CUDA cores, any sizes and both storage types (the true 32-bit path)
 //   moe_combine        one block per token, 32-bit sum in the order of the choices
 #include "common.cuh"
 
 #define ROUTE_WARPS 4
+#define ROUTE_TOKENS 4        // tokens per block: a router row is read once for all of them
 
 template <typename A>
 __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restrict__ router,
                                  const float* __restrict__ correction, int* __restrict__ ids,
                                  float* __restrict__ weights, int T, int W, int N, int top) {
-    extern __shared__ float sm[];                 // per warp: N scores, N choice scores
+    extern __shared__ float sm[];                 // per token of the block: N scores, N choice scores
     pdl_wait();
     pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * ROUTE_WARPS + warp;
-    if (t >= T) return;
-    float* s = sm + (size_t)warp * 2 * N;
-    float* c = s + N;
-    const A* h = x + (size_t)t * W;
-    for (int n = 0; n < N; ++n) {
+    const int t0 = blockIdx.x * ROUTE_TOKENS;
+    const int nt = min(ROUTE_TOKENS, T - t0);
+    float* base = sm;
+    for (int n = warp; n < N; n += ROUTE_WARPS) {
         const float* wr = router + (size_t)n * W;
-        float dot = 0.f;
-        for (int i = lane; i < W; i += 32) dot += wr[i] * to_f32(h[i]);
-        dot = warp_sum(dot);
-        if (lane == 0) s[n] = dot;
-    }
-    __syncwarp();
-    float mx = -INFINITY;
-    for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int n = lane; n < N; n += 32) { const float e = expf(s[n] - mx); s[n] = e; sum += e; }
-    sum = warp_sum(sum);
-    const float inv = 1.f / sum;
-    for (int n = lane; n < N; n += 32) { const float p = s[n] * inv; s[n] = p; c[n] = p + correction[n]; }
-    __syncwarp();
-    float chosen_sum = 0.f;
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int arg = N;
-        for (int n = lane; n < N; n += 32)
-            if (c[n] > best) { best = c[n]; arg = n; }         // the lowest index among a lane's equals
+        float dot[ROUTE_TOKENS];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+        for (int j = 0; j < ROUTE_TOKENS; ++j) dot[j] = 0.f;
+        for (int i = lane; i < W; i += 32) {
+            const float r = wr[i];
+#pragma unroll
+            for (int j = 0; j < ROUTE_TOKENS; ++j)
+                if (j < nt) dot[j] += r * to_f32(x[(size_t)(t0 + j) * W + i]);
         }
-        if (arg >= N) arg = 0;                                  // only if every score is NaN or -inf
-        const float p = s[arg];
-        chosen_sum += p;
-        if (lane == 0) {
-            ids[(size_t)t * top + k] = arg;
-            weights[(size_t)t * top + k] = p;
-            c[arg] = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < ROUTE_TOKENS; ++j) {
+            const float d = warp_sum(dot[j]);
+            if (lane == 0) base[(size_t)j * 2 * N + n] = d;
         }
+    }
+    __syncthreads();
+    for (int j = warp; j < nt; j += ROUTE_WARPS) {
+        const int t = t0 + j;
+        float* s = base + (size_t)j * 2 * N;
+        float* c = s + N;
+        float mx = -INFINITY;
+        for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int n = lane; n < N; n += 32) { const float e = expf(s[n] - mx); s[n] = e; sum += e; }
+        sum = warp_sum(sum);
+        const float inv = 1.f / sum;
+        for (int n = lane; n < N; n += 32) { const float p = s[n] * inv; s[n] = p; c[n] = p + correction[n]; }
+        __syncwarp();
+        float chosen_sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int arg = N;
+            for (int n = lane; n < N; n += 32)
+                if (c[n] > best) { best = c[n]; arg = n; }         // the lowest index among a lane's equals
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+                if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+            }
+            if (arg >= N) arg = 0;                                  // only if every score is NaN or -inf
+            const float p = s[arg];
+            chosen_sum += p;
+            if (lane == 0) {
+                ids[(size_t)t * top + k] = arg;
+                weights[(size_t)t * top + k] = p;
+                c[arg] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        const float norm = 1.f / (chosen_sum + 1e-20f);
+        for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] *= norm;
         __syncwarp();
     }
-    const float norm = 1.f / (chosen_sum + 1e-20f);
-    if (lane < top) weights[(size_t)t * top + lane] *= norm;
-    for (int k = 32 + lane; k < top; k += 32) weights[(size_t)t * top + k] *= norm;
 }
 
 extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const float* correction, int* ids,
                             float* weights, int T, int W, int N, int top, void* stream) {
     if (T <= 0) return 0;
     if (top < 1 || top > N) return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)ROUTE_WARPS * 2 * N * sizeof(float);
+    const size_t smem = (size_t)ROUTE_TOKENS * 2 * N * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((T + ROUTE_WARPS - 1) / ROUTE_WARPS), block(ROUTE_WARPS * 32);
+    dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(ROUTE_WARPS * 32);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(moe_route_kernel<bf16>, grid, block, smem, s, 1, (const bf16*)x, router, correction, ids,
                          weights, T, W, N, top);
@@ -281,4 +295,155 @@ extern "C" int rg_moe_combine(const void* x, const void* y, const void* shared, 
         return rg_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (const float*)x, (const float*)y,
                          (const float*)shared, ids, weights, pair_pos, out, W, E, top);
     return RG_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// The same product on the tensor cores (bfloat16, mma.sync m16n8k16, 32-bit accumulators): one block per
+// (tile of BM places of one expert, 64 output columns), the expert's rows W[n0 .. n0 + 64) and the tile's
+// gathered input rows streamed through a three-stage cp.async ring in steps of 64 along K.  With few places
+// per expert (decode) the block is a weight-streaming product whose tile is mostly padding; with many
+// (prompts) BM = 128 places share every weight row that is read.  GATED: gate and up rows side by side,
+// silu(gate) * up in the epilogue, in 32-bit.  K and lda must be multiples of 8 (16-byte copies).
+#include "mma.cuh"
+
+#define GM_BN 64
+#define GM_BK 64
+#define GM_STAGES 3
+#define GM_STRIDE (GM_BK + 8)
+
+template <int BM, bool GATED>
+__global__ void __launch_bounds__(BM == 128 ? 256 : 128) moe_grouped_gemm_mma_kernel(
+        const bf16* __restrict__ a, int lda, const int* __restrict__ src, int src_div, const bf16* __restrict__ w,
+        bf16* __restrict__ out, int ldo, const int* __restrict__ tiles, int N, int K) {
+    using namespace rgmma;
+    constexpr int THREADS = BM == 128 ? 256 : 128;
+    constexpr int WARPS_M = BM == 128 ? 4 : 2;                     // x 2 warps along the columns
+    constexpr int WM = BM / WARPS_M;                               // rows per warp: 32 or 16
+    constexpr int MI = WM / 16;
+    constexpr int NB = GATED ? 2 : 1;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* sA = reinterpret_cast<bf16*>(smem_raw);                  // [STAGES][BM][STRIDE]
+    bf16* sB = sA + GM_STAGES * BM * GM_STRIDE;                    // [STAGES][NB][BN][STRIDE]
+    __shared__ int rowsrc[BM];
+    pdl_wait();
+    pdl_trigger();
+    const int* tl = tiles + 3 * (size_t)blockIdx.x;
+    const int e = tl[0], first = tl[1], nrows = tl[2];
+    if (e < 0) return;
+    const int n0 = blockIdx.y * GM_BN;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int r = tid; r < BM; r += THREADS) rowsrc[r] = r < nrows ? (src ? src[first + r] / src_div : first + r) : -1;
+    __syncthreads();
+    const bf16* we = w + (size_t)e * NB * N * K;
+    const int ksteps = (K + GM_BK - 1) / GM_BK;
+
+    auto load_stage = [&](int ks, int stage) {
+        const int k0 = ks * GM_BK;
+        bf16* dA = sA + stage * BM * GM_STRIDE;
+        for (int i = tid; i < BM * (GM_BK / 8); i += THREADS) {
+            const int r = i >> 3, c = (i & 7) * 8;
+            const int row = rowsrc[r];
+            const bool valid = row >= 0 && k0 + c < K;
+            cp_async16(dA + r * GM_STRIDE + c, valid ? a + (size_t)row * lda + k0 + c : a, valid);
+        }
+        bf16* dB = sB + stage * NB * GM_BN * GM_STRIDE;
+        for (int i = tid; i < NB * GM_BN * (GM_BK / 8); i += THREADS) {
+            const int half = i / (GM_BN * 8), j = i - half * GM_BN * 8;
+            const int n = j >> 3, c = (j & 7) * 8;
+            const bool valid = n0 + n < N && k0 + c < K;
+            cp_async16(dB + (half * GM_BN + n) * GM_STRIDE + c,
+                       valid ? we + ((size_t)half * N + n0 + n) * K + k0 + c : we, valid);
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < GM_STAGES - 1; ++s) {
+        if (s < ksteps) load_stage(s, s);
+        cp_async_commit();
+    }
+    const int wm = warp >> 1, wn = warp & 1;                       // warp tile: rows wm * WM, columns wn * 32
+    const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
+    const int b_row = (lane & 7) + (lane >> 4) * 8, b_col = ((lane >> 3) & 1) * 8;
+    float acc[NB][MI][4][4];
+#pragma unroll
+    for (int h = 0; h < NB; ++h)
+#pragma unroll
+        for (int mi = 0; mi < MI; ++mi)
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) { acc[h][mi][ni][0] = acc[h][mi][ni][1] = acc[h][mi][ni][2] = acc[h][mi][ni][3] = 0.f; }
+
+    for (int ks = 0; ks < ksteps; ++ks) {
+        cp_async_wait<GM_STAGES - 2>();
+        __syncthreads();
+        if (ks + GM_STAGES - 1 < ksteps) load_stage(ks + GM_STAGES - 1, (ks + GM_STAGES - 1) % GM_STAGES);
+        cp_async_commit();
+        const bf16* cA = sA + (ks % GM_STAGES) * BM * GM_STRIDE;
+        const bf16* cB = sB + (ks % GM_STAGES) * NB * GM_BN * GM_STRIDE;
+#pragma unroll
+        for (int kk = 0; kk < GM_BK / 16; ++kk) {
+            uint32_t af[MI][4];
+#pragma unroll
+            for (int mi = 0; mi < MI; ++mi)
+                ldmatrix_x4(af[mi], cA + (wm * WM + mi * 16 + a_row) * GM_STRIDE + kk * 16 + a_col);
+#pragma unroll
+            for (int h = 0; h < NB; ++h) {
+#pragma unroll
+                for (int n2 = 0; n2 < 2; ++n2) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, cB + (h * GM_BN + wn * 32 + n2 * 16 + b_row) * GM_STRIDE + kk * 16 + b_col);
+#pragma unroll
+                    for (int mi = 0; mi < MI; ++mi) {
+                        mma_bf16(acc[h][mi][2 * n2], af[mi], b[0], b[1]);
+                        mma_bf16(acc[h][mi][2 * n2 + 1], af[mi], b[2], b[3]);
+                    }
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+    const int g = lane >> 2, tq = lane & 3;
+#pragma unroll
+    for (int mi = 0; mi < MI; ++mi) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * WM + mi * 16 + g + half * 8;
+            if (r >= nrows) continue;
+            bf16* orow = out + (size_t)(first + r) * ldo;
+#pragma unroll
+            for (int ni = 0; ni < 4; ++ni) {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int n = n0 + wn * 32 + ni * 8 + tq * 2 + c;
+                    if (n >= N) continue;
+                    float v = acc[0][mi][ni][half * 2 + c];
+                    if (GATED) v = v / (1.f + expf(-v)) * acc[NB - 1][mi][ni][half * 2 + c];
+                    orow[n] = __float2bfloat16_rn(v);
+                }
+            }
+        }
+    }
+}
+
+template <typename KF> static int gm_allow_smem(KF kernel, size_t bytes) {
+    return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+// tile_rows: 32 or 128, the tile size `moe_align` was given.
+extern "C" int rg_moe_grouped_gemm_mma(const void* a, int lda, const int* src, int src_div, const void* w, void* out,
+                                       int ldo, const int* tiles, int max_tiles, int tile_rows, int N, int K,
+                                       int gated, void* stream) {
+    if (max_tiles <= 0 || N <= 0) return 0;
+    if ((tile_rows != 32 && tile_rows != 128) || K < 8 || (K & 7) || (lda & 7) || src_div < 1) return RG_ERR_UNSUPPORTED;
+    if (((uintptr_t)a | (uintptr_t)w) & 15) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(max_tiles, (N + GM_BN - 1) / GM_BN);
+    int e;
+#define RG_GM(BM, G) { const size_t smem = (size_t)GM_STAGES * (BM + (G ? 2 : 1) * GM_BN) * GM_STRIDE * 2; \
+        e = gm_allow_smem(moe_grouped_gemm_mma_kernel<BM, G>, smem); if (e) return e; \
+        return rg_launch(moe_grouped_gemm_mma_kernel<BM, G>, grid, dim3(BM == 128 ? 256 : 128), smem, s, 1, \
+                         (const bf16*)a, lda, src, src_div, (const bf16*)w, (bf16*)out, ldo, tiles, N, K); }
+    if (tile_rows == 32 && gated) RG_GM(32, true)
+    if (tile_rows == 32 && !gated) RG_GM(32, false)
+    if (tile_rows == 128 && gated) RG_GM(128, true)
+    RG_GM(128, false)
+#undef RG_GM
 }

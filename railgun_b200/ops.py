@@ -263,6 +263,52 @@ def latent_attention_general(qa: torch.Tensor, cache: torch.Tensor, block_table:
     return out
 
 
+def latent_attention_mma_ok(dtype, H: int, R: int, D: int) -> bool:
+    """Whether the tensor-core kernels take these sizes: bfloat16, latent and row sizes in steps of 16, a latent
+    of at most 512 numbers, a row that fits shared memory."""
+    if dtype != torch.bfloat16 or R % 16 or D % 16 or not 16 <= R <= 512 or D < R:
+        return False
+    return (64 + 64) * (D + 8) * 2 + 4 * 16 * 40 * 2 + 4 * 64 * 4 <= 227 * 1024
+
+
+def latent_decode_splits(n_tokens: int, head_chunks: int, max_context: int) -> int:
+    """How many shares a single token's context is cut into: enough blocks to fill the device twice, at least
+    128 keys a share."""
+    by_residency = 296 // max(1, n_tokens * head_chunks)
+    by_length = -(-max_context // 128)
+    return max(1, min(by_residency, by_length, 64))
+
+
+def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tiles,
+                         rows, n_items: int, req_of_token: torch.Tensor, positions: torch.Tensor, R: int, window: int,
+                         scale: float, num_splits: int = 1) -> None:
+    """Attention over the latent cache on the tensor cores, into ``out`` [T, H, R].  With ``tiles`` [n, 3]
+    (first row, rows <= 64, request): requests with several tokens.  Without: ``n_items`` single tokens
+    (``rows``, or rows 0..n_items-1), every context cut into ``num_splits`` shares that a second kernel adds."""
+    _check(qa, "qa", torch.bfloat16)
+    _check(out, "out", torch.bfloat16)
+    _check(cache, "cache", torch.bfloat16)
+    _check(block_table, "block_table", torch.int32)
+    _check(req_of_token, "req_of_token", torch.int32)
+    _check(positions, "positions", torch.int32)
+    T, H, D = qa.shape
+    if cache.dim() != 3 or cache.shape[2] != D or out.shape != (T, H, R) or not latent_attention_mma_ok(qa.dtype, H, R, D):
+        raise KernelError(f"latent_attention_mma: queries {tuple(qa.shape)}, cache {tuple(cache.shape)}, latent {R}")
+    for t, name in ((tiles, "tiles"), (rows, "rows")):
+        if t is not None:
+            _check(t, name, torch.int32)
+    part_o = part_ml = None
+    if tiles is None and num_splits > 1:
+        part_o = torch.empty((T, H, num_splits, R), dtype=torch.float32, device=qa.device)
+        part_ml = torch.empty((T, H, num_splits, 2), dtype=torch.float32, device=qa.device)
+        _COUNTER.value += 1                                   # the kernel that adds the shares
+    _ok(_fn("attention_latent_mma", "rg_latent_attention_mma")(
+        _ptr(qa), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(cache), _ptr(block_table), c_int(block_table.shape[1]),
+        _ptr(tiles), _ptr(rows), c_int(n_items), _ptr(req_of_token), _ptr(positions), c_int(H), c_int(R), c_int(D),
+        c_int(cache.shape[1]), c_int(window or 0), c_float(scale), c_int(num_splits if tiles is None else 1),
+        _stream()), "latent_attention_mma")
+
+
 MOE_TILE_ROWS = 32
 
 
@@ -307,7 +353,9 @@ def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles:
     expert; ``w`` [E, N, K] (``gated``: [E, 2 N, K] = gate rows then up rows and
     out = silu(gate) * up).  Row ``pos`` of the input is ``a[src[pos] // src_div]``
     or, without ``src``, ``a[pos]``.  Returns [places, N]; rows that belong to no
-    tile are not written."""
+    tile are not written.  bfloat16 with rows on 16-byte boundaries runs on the
+    tensor cores (tiles of 32 or 128 places), everything else in 32-bit
+    arithmetic on the CUDA cores (tiles of 32)."""
     _check(a, "a")
     _check(w, "w", a.dtype)
     _check(tiles, "tiles", torch.int32)
@@ -318,11 +366,29 @@ def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles:
     if a.shape[1] != K or (gated and rows_w % 2):
         raise KernelError(f"moe_grouped_gemm: a {tuple(a.shape)} vs w {tuple(w.shape)}")
     out = torch.empty((places, N), dtype=a.dtype, device=a.device)
+    if moe_grouped_gemm_tc_ok(a.dtype, K, a.stride(0)):
+        _ok(_fn("moe", "rg_moe_grouped_gemm_mma")(
+            _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), _ptr(tiles),
+            c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0), _stream()),
+            "moe_grouped_gemm_mma")
+        return out
     _ok(_fn("moe", "rg_moe_grouped_gemm")(
         _ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(w), _ptr(out), c_int(N), c_int(_dtype_code(a)),
         _ptr(tiles), c_int(tiles.shape[0]), c_int(tile_rows), c_int(N), c_int(K), c_int(1 if gated else 0), _stream()),
         "moe_grouped_gemm")
     return out
+
+
+def moe_grouped_gemm_tc_ok(dtype, K: int, lda: int) -> bool:
+    """Whether the grouped product runs on the tensor cores: bfloat16, rows that start on 16-byte boundaries."""
+    return dtype == torch.bfloat16 and K % 8 == 0 and lda % 8 == 0 and K >= 8
+
+
+def moe_tile_rows(dtype, pairs: int, num_experts: int, K1: int, K2: int) -> int:
+    """Places per tile of the grouped products: 128 on the tensor cores once an expert gets 64 places on
+    average (prompts: every weight row that is read serves 128 rows), else 32."""
+    tc = moe_grouped_gemm_tc_ok(dtype, K1, K1) and moe_grouped_gemm_tc_ok(dtype, K2, K2)
+    return 128 if tc and pairs >= 64 * max(1, num_experts) else MOE_TILE_ROWS
 
 
 def moe_combine(x: torch.Tensor, y, shared, ids: torch.Tensor, weights: torch.Tensor, pair_pos: torch.Tensor,

@@ -103,9 +103,28 @@ class LatentAttention(Mixer):
         return ops.linear(heads, self.w_o)
 
     def attend(self, qa, batch, cache):
+        """bfloat16 with sizes in steps of 16 runs on the tensor cores (requests with several tokens in tiles of
+        64 / heads tokens, single tokens with their contexts cut into shares); everything else, and all of the
+        32-bit path, through the general kernel."""
         table = batch.block_table[cache.group]
-        return ops.latent_attention_general(qa, cache.kv, table, batch.req_of_token, batch.positions, self.R,
-                                            self.window, self.scale)
+        if not ops.latent_attention_mma_ok(qa.dtype, self.H, self.R, self.D):
+            return ops.latent_attention_general(qa, cache.kv, table, batch.req_of_token, batch.positions, self.R,
+                                                self.window, self.scale)
+        out = torch.empty((qa.shape[0], self.H, self.R), dtype=qa.dtype, device=qa.device)
+        chunks = -(-self.H // 64)
+        args = (batch.req_of_token, batch.positions, self.R, self.window, self.scale)
+        if batch.decode_only:
+            n = batch.num_tokens
+            ops.latent_attention_mma(qa, out, cache.kv, table, None, None, n, *args,
+                                     ops.latent_decode_splits(n, chunks, batch.max_context_len))
+            return out
+        if batch.num_prefill_tiles:
+            ops.latent_attention_mma(qa, out, cache.kv, table, batch.prefill_tiles, None, batch.num_prefill_tiles, *args)
+        if batch.num_decode_rows:
+            n = batch.num_decode_rows
+            ops.latent_attention_mma(qa, out, cache.kv, table, None, batch.decode_rows, n, *args,
+                                     ops.latent_decode_splits(n, chunks, batch.max_context_len))
+        return out
 
 
 register_mixer("latent_attention", LatentAttention)

@@ -71,10 +71,11 @@ class RoutedExperts(FeedForward):
         ids, weights = ops.moe_route(x, self.router, self.correction, self.top)
         y = pair_pos = None
         if self.E:
-            sorted_pair, pair_pos, tiles = ops.moe_align(ids, self.E)
             places = T * self.top
-            act = ops.moe_grouped_gemm(x, sorted_pair, self.top, self.w_gate_up, tiles, places, gated=True)
-            y = ops.moe_grouped_gemm(act, None, 1, self.w_down, tiles, places, gated=False)
+            rows = ops.moe_tile_rows(x.dtype, places, self.E, self.w_gate_up.shape[2], self.w_down.shape[2])
+            sorted_pair, pair_pos, tiles = ops.moe_align(ids, self.E, rows)
+            act = ops.moe_grouped_gemm(x, sorted_pair, self.top, self.w_gate_up, tiles, places, True, rows)
+            y = ops.moe_grouped_gemm(act, None, 1, self.w_down, tiles, places, False, rows)
         else:
             pair_pos = ids
         shared = self.shared.forward(x, batch) if self.shared is not None else None

@@ -80,6 +80,19 @@ def route(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: 
     return chosen, picked / (picked.sum(dim=-1, keepdim=True) + 1e-20)
 
 
+def route_margin(h: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int) -> torch.Tensor:
+    """How far each token's choice is from a tie [T]: the gap between the last
+    chosen and the first unchosen corrected score, relative to the sum of the
+    two experts' scores (infinite when every router output is chosen).  A model
+    in reduced precision may choose differently where this is small."""
+    scores = torch.softmax(h @ router.T, dim=-1)
+    if top >= scores.shape[-1]:
+        return torch.full((h.shape[0],), math.inf, dtype=h.dtype)
+    order = torch.sort(scores + correction, dim=-1, descending=True)
+    pair = torch.gather(scores, 1, order.indices[:, top - 1:top + 1])
+    return (order.values[:, top - 1] - order.values[:, top]) / pair.sum(dim=-1)
+
+
 def expert_mixture(h: torch.Tensor, w: dict, p: dict) -> torch.Tensor:
     """Routed experts plus an always-on shared one.  The last ``identity``
     router outputs stand for experts that return their input."""
@@ -121,14 +134,17 @@ def layer_order(cfg: dict) -> list:
     return order
 
 
-def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, return_layers: bool = False):
+def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, return_layers: bool = False,
+            return_margins: bool = False):
     """Logits [T, vocab] of one whole sequence (and the residual stream after
-    every layer run)."""
+    every layer run, or each position's smallest ``route_margin`` over all
+    feed-forwards that ran)."""
     t = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in tensors.items()}
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x0 = t["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     x = x0
     trail = []
+    margins = torch.full((x.shape[0],), math.inf, dtype=dtype)
     for i, starts_pass in layer_order(cfg):
         L = cfg["layers"][i]
         pre = f"l{i}."
@@ -139,10 +155,15 @@ def forward(cfg: dict, tensors: dict, tokens, dtype=torch.float64, return_layers
         x = x + m * (rms_norm(y, t[pre + "norm1b"], eps) * t[pre + "ls1"])
         if L.get("mlp"):
             assert L["mlp"]["kind"] == "moe"
-            y = expert_mixture(rms_norm(x, t[pre + "norm2"], eps), sub(t, pre + "mlp."), L["mlp"])
+            h2 = rms_norm(x, t[pre + "norm2"], eps)
+            margins = torch.minimum(margins, route_margin(h2, t[pre + "mlp.router"], t[pre + "mlp.correction"],
+                                                          L["mlp"]["router"]["top"]))
+            y = expert_mixture(h2, sub(t, pre + "mlp."), L["mlp"])
             x = x + m * (rms_norm(y, t[pre + "norm2b"], eps) * t[pre + "ls2"])
         trail.append(x)
     logits = softcap(rms_norm(x, t["final.norm"], eps) @ t["head"].T, cfg["logit_softcap"])
+    if return_margins:
+        return logits, margins
     return (logits, torch.stack(trail)) if return_layers else logits
 
 
@@ -160,9 +181,9 @@ class PlainDizatar:
         self.cfg = json.loads((model_dir / "config.json").read_text())
         self.tensors = {k: torch.from_numpy(v) for k, v in read_safetensors(model_dir / "model.safetensors").items()}
 
-    def forward(self, tokens, return_layers: bool = False):
-        out = forward(self.cfg, self.tensors, tokens, torch.float64, return_layers)
-        return (out[0].numpy(), out[1].numpy()) if return_layers else out.numpy()
+    def forward(self, tokens, return_layers: bool = False, return_margins: bool = False):
+        out = forward(self.cfg, self.tensors, tokens, torch.float64, return_layers, return_margins)
+        return (out[0].numpy(), out[1].numpy()) if return_layers or return_margins else out.numpy()
 
     def greedy(self, prompt, n: int) -> list:
         toks = list(prompt)
