@@ -92,13 +92,18 @@ class ClockSampler:
 
 def model_folder(cfg_dict, seed=0):
     """The model folder with random weights (written once per machine into the temporary folder)."""
-    from railgun_b200.config.llama import LlamaConfig
+    from railgun_b200.config.registry import architecture_name, architecture_of
     from railgun_b200.weights.random_init import write_random_model
-    tag = f"rg_bench_L{cfg_dict['num_hidden_layers']}_H{cfg_dict['hidden_size']}_V{cfg_dict['vocab_size']}_s{seed}"
+    if "hidden_size" in cfg_dict:
+        tag = f"rg_bench_L{cfg_dict['num_hidden_layers']}_H{cfg_dict['hidden_size']}_V{cfg_dict['vocab_size']}_s{seed}"
+    else:
+        import hashlib
+        tag = f"rg_bench_{hashlib.sha1(json.dumps(cfg_dict, sort_keys=True).encode()).hexdigest()[:12]}_s{seed}"
     d = os.path.join(tempfile.gettempdir(), tag)
     if not (os.path.exists(os.path.join(d, "model.safetensors")) and os.path.exists(os.path.join(d, "config.json"))):
         tmp = d + f".tmp{os.getpid()}"
-        write_random_model(LlamaConfig.from_dict(cfg_dict), seed, tmp)
+        config = architecture_of(architecture_name(cfg_dict)).config_from_dict(cfg_dict)
+        write_random_model(config, seed, tmp)
         if os.path.exists(d):
             import shutil
             shutil.rmtree(d, ignore_errors=True)
@@ -124,28 +129,13 @@ def prefill_flops(cfg, T):
     return linear + attn + 2 * V * H
 
 
-def run_ours(args):
+def decode_tools(runner, V, rng):
+    """``fill_contexts``, ``DecodeLoop`` and ``time_decode`` over one runner: the decode steps that generation
+    launches, timed in windows with CUDA events."""
     import numpy as np
     import torch
     from railgun_b200.engine.batch import StepEntry
-    from railgun_b200.engine.engine import Engine
-    from railgun_b200.engine.request import SamplingParams
     from railgun_b200 import ops
-
-    cfg = dict(LLAMA_3_2_1B)
-    full_layers = cfg["num_hidden_layers"]
-    if args.layers:
-        cfg["num_hidden_layers"] = args.layers
-    pk, pk_src = peaks()
-    mdir = model_folder(cfg)
-    page = 16
-    pool_tokens = 64 * 8192                                # the cache pool: 64 sequences x 8,192 tokens
-    eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
-                 max_num_batched_tokens=8192, max_model_len=8192)
-    runner = eng.runner
-    V = cfg["vocab_size"]
-    rng = np.random.default_rng(0)
-    kv_per_token = runner.cache.bytes_per_token()
     launches = ops.launch_counter()
 
     def fill_contexts(batch, first_id, context=CONTEXT):
@@ -215,6 +205,35 @@ def run_ours(args):
         runner.end(ids.tolist())
         ms = sorted(windows)[len(windows) // 2]
         return batch / ms * 1e3, ms, n_launch, len(windows)
+
+    return fill_contexts, DecodeLoop, time_decode
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    from railgun_b200.engine.batch import StepEntry
+    from railgun_b200.engine.engine import Engine
+    from railgun_b200.engine.request import SamplingParams
+    from railgun_b200 import ops
+
+    cfg = dict(LLAMA_3_2_1B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk, pk_src = peaks()
+    mdir = model_folder(cfg)
+    page = 16
+    pool_tokens = 64 * 8192                                # the cache pool: 64 sequences x 8,192 tokens
+    eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
+                 max_num_batched_tokens=8192, max_model_len=8192)
+    runner = eng.runner
+    V = cfg["vocab_size"]
+    rng = np.random.default_rng(0)
+    kv_per_token = runner.cache.bytes_per_token()
+    launches = ops.launch_counter()
+
+    fill_contexts, DecodeLoop, time_decode = decode_tools(runner, V, rng)
 
     def hbm_frac(batch, ms, steps, warmup, context=CONTEXT):
         bytes_step = decode_bytes(cfg, batch, context + warmup + steps // 2, kv_per_token)
@@ -363,6 +382,73 @@ def run_ours(args):
     return 0
 
 
+def dizatar_sizes(name):
+    """(Dizatar configuration, the Llama configuration of equal width, layer runs and vocabulary beside it)."""
+    def diz(width, heads, dim, rot, vdim, rank, experts, identity, top, ff, shared, vocab):
+        layer = dict(type="latent_attention",
+                     mixer=dict(heads=heads, dim=dim, rot_dim=rot, vdim=vdim, kv_rank=rank, scale=(dim + rot) ** -0.5,
+                                rot=dict(base=10000.0, dims=rot)),
+                     mlp=dict(kind="moe", router=dict(experts=experts, identity=identity, top=top), expert=dict(ff=ff),
+                              shared=dict(ff=shared)))
+        return dict(architecture="Dizatar", width=width, vocab=vocab, norm=dict(eps=1e-6), residual_mult=0.7,
+                    logit_softcap=30.0, loop=dict(start=1, stop=3, times=2), layers=[layer] * 4)
+
+    def llama(width, heads, kv, ff, vocab, runs):
+        return dict(architectures=["LlamaForCausalLM"], hidden_size=width, num_attention_heads=heads,
+                    num_key_value_heads=kv, head_dim=64, num_hidden_layers=runs, intermediate_size=ff, vocab_size=vocab,
+                    rope_theta=500000.0, rope_scaling=None, tie_word_embeddings=True, rms_norm_eps=1e-5,
+                    max_position_embeddings=131072, torch_dtype="bfloat16")
+
+    if name == "w2048":      # 16 heads of 128 + 64 over a latent of 512; 32 experts of 1,024, 4 of 34 chosen
+        return diz(2048, 16, 128, 64, 128, 512, 32, 2, 4, 1024, 2048, 32768), llama(2048, 32, 8, 8192, 32768, 6)
+    if name == "w1024":      # 8 heads of 64 + 32 over a latent of 256; 16 experts of 512, 2 of 17 chosen
+        return diz(1024, 8, 64, 32, 64, 256, 16, 1, 2, 512, 1024, 32768), llama(1024, 16, 4, 4096, 32768, 6)
+    raise ValueError(name)
+
+
+def run_dizatar(args):
+    """Prefill and decode throughput of Dizatar at layer sizes of real models (random weights), beside the dense
+    GQA Llama of equal width, number of layer runs and vocabulary.  One JSON line per model and size."""
+    import numpy as np
+    import torch
+    from railgun_b200.engine.batch import StepEntry
+    from railgun_b200.engine.engine import Engine
+    page, pool_tokens = 16, 64 * 4096
+    for size in (args.sizes.split(",") if args.sizes else ["w1024", "w2048"]):
+        for label, cfg in zip(("dizatar", "llama"), dizatar_sizes(size)):
+            mdir = model_folder(cfg)
+            eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
+                         max_num_batched_tokens=8192, max_model_len=4096)
+            runner = eng.runner
+            V = cfg.get("vocab", cfg.get("vocab_size"))
+            rng = np.random.default_rng(0)
+            _, _, time_decode = decode_tools(runner, V, rng)
+            line = {"mode": "dizatar", "size": size, "model": label, "layer_runs": len(runner.model.order),
+                    "cache_bytes_per_token": runner.cache.bytes_per_token()}
+            for b in (8, 64):
+                tok_s, ms, n_launch, _ = time_decode(b, args.steps, args.warmup, 1000 * b, args.context)
+                line[f"decode_b{b}_tok_s"], line[f"decode_b{b}_ms"] = round(tok_s, 1), round(ms, 4)
+                line[f"decode_b{b}_launches_per_step"] = n_launch // args.steps
+            prompt = rng.integers(0, V, size=args.tokens).tolist()
+            times = []
+            for i in range(args.warmup + 7):
+                torch.cuda.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                runner.step([StepEntry(7000 + i, prompt, [args.tokens - 1])])
+                t1.record()
+                torch.cuda.synchronize()
+                runner.end([7000 + i])
+                times.append(t0.elapsed_time(t1))
+            runner.check_device_errors()
+            ms = sorted(times[args.warmup:])[len(times[args.warmup:]) // 2]
+            line.update(prefill_tokens=args.tokens, prefill_ms=round(ms, 3), prefill_tok_s=round(args.tokens / ms * 1e3, 1))
+            print(json.dumps(line), flush=True)
+            del eng, runner, time_decode
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_kernels(args):
     """Times the hot kernels one by one, each as a CUDA graph of 16 calls over 16 different operand sets (so
     that weights and caches come from HBM, not L2), with CUDA events around replays.  One JSON line per case."""
@@ -497,6 +583,89 @@ def run_kernels(args):
             us = timed(lambda: [ops.prefill_attention_tc(q, o, kv, bt, t128, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
             us2 = timed(lambda: [ops.prefill_attention(q, QKV, o, kv, bt, t64, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
             out(f"prefill attention T{T} tcgen05", us, TFLOPs=round(fl / us / 1e6, 1), mma_sync_us=round(us2, 2))
+    if on("latent_attention"):
+        # attention over the latent cache (16 heads, latent 512 + 64) beside the dense model's kernels at equal
+        # width; decode: bytes of cache read per second, prompts: FLOP/s of the products the kernel does
+        pk, _ = peaks()
+        Hh, R, dr = 16, 512, 64
+        D = R + dr
+        for B, ctx in ((8, 1024), (64, 1024), (8, 8192)):
+            blocks = -(-ctx // page)
+            caches = [torch.randn(B * blocks, page, D, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(B * blocks, dtype=torch.int32, device=dev).view(B, blocks).contiguous()
+            qa = torch.randn(B, Hh, D, device=dev).to(torch.bfloat16)
+            o = torch.empty(B, Hh, R, dtype=torch.bfloat16, device=dev)
+            req = torch.arange(B, dtype=torch.int32, device=dev)
+            pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+            sp = ops.latent_decode_splits(B, 1, ctx)
+            us = timed(lambda: [ops.latent_attention_mma(qa, o, c, bt, None, None, B, req, pos, R, 0, D ** -0.5, sp) for c in caches])
+            kvs = [torch.randn(B * blocks, 2, nkv, page, d, device=dev).to(torch.bfloat16) for _ in range(L)]
+            q = torch.randn(B, QKV, device=dev).to(torch.bfloat16)
+            o2 = torch.empty(B, nh * d, dtype=torch.bfloat16, device=dev)
+            sp2 = ops.decode_splits(B, nkv, ctx)
+            us2 = timed(lambda: [ops.decode_attention(q, QKV, o2, kv, bt, None, B, req, pos, nh, nkv, d, 0, d ** -0.5, sp2) for kv in kvs])
+            gbs, gbs2 = B * ctx * D * 2 / us / 1e3, B * ctx * nkv * d * 4 / us2 / 1e3
+            out(f"latent decode attention B{B} ctx{ctx} splits{sp}", us, GBs=round(gbs, 1), frac=round(gbs / pk["hbm_gbs"], 3),
+                llama_us=round(us2, 2), llama_GBs=round(gbs2, 1), llama_frac=round(gbs2 / pk["hbm_gbs"], 3))
+        for T in (2048, 8192):
+            blocks = -(-T // page)
+            caches = [torch.randn(blocks, page, D, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(blocks, dtype=torch.int32, device=dev).view(1, blocks).contiguous()
+            qa = torch.randn(T, Hh, D, device=dev).to(torch.bfloat16)
+            o = torch.empty(T, Hh, R, dtype=torch.bfloat16, device=dev)
+            pos = torch.arange(T, dtype=torch.int32, device=dev)
+            req = torch.zeros(T, dtype=torch.int32, device=dev)
+            t64 = torch.tensor([(k, min(64, T - k), 0) for k in range(0, T, 64)], dtype=torch.int32, device=dev)
+            us = timed(lambda: [ops.latent_attention_mma(qa, o, c, bt, t64, None, t64.shape[0], req, pos, R, 0, D ** -0.5) for c in caches])
+            fl = Hh * 2 * (D + R) * T * (T + 1) / 2
+            kvs = [torch.randn(blocks, 2, nkv, page, d, device=dev).to(torch.bfloat16) for _ in range(L)]
+            q = torch.randn(T, QKV, device=dev).to(torch.bfloat16)
+            o2 = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+            t128 = torch.tensor([(k, min(128, T - k), 0) for k in range(0, T, 128)], dtype=torch.int32, device=dev)
+            fl2 = nh * 4 * d * T * (T + 1) / 2
+            us2 = timed(lambda: [ops.prefill_attention_tc(q, o2, kv, bt, t128, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
+            us3 = timed(lambda: [ops.prefill_attention(q, QKV, o2, kv, bt, t64, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
+            out(f"latent prompt attention T{T}", us, TFLOPs=round(fl / us / 1e6, 1), frac=round(fl / us / 1e6 / pk["bf16_tflops"], 3),
+                llama_tcgen05_us=round(us2, 2), llama_tcgen05_TFLOPs=round(fl2 / us2 / 1e6, 1),
+                llama_tcgen05_frac=round(fl2 / us2 / 1e6 / pk["bf16_tflops"], 3),
+                llama_mma_sync_us=round(us3, 2), llama_mma_sync_TFLOPs=round(fl2 / us3 / 1e6, 1))
+    if on("moe"):
+        # the routed experts' two grouped products (32 experts of 1,024 at width 2,048, 4 choices) beside the dense
+        # model's gate|up and down products of equal work: decode by bytes of weights read, prompts by FLOP/s
+        pk, _ = peaks()
+        E, F, top = 32, 1024, 4
+        for T in (8, 64, 2048, 8192):
+            x = torch.randn(T, H, device=dev).to(torch.bfloat16)
+            wgu = [(torch.randn(E, 2 * F, H, device=dev) / H ** 0.5).to(torch.bfloat16) for _ in range(L)]
+            wd = [(torch.randn(E, H, F, device=dev) / F ** 0.5).to(torch.bfloat16) for _ in range(L)]
+            ids = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(T)]).to(torch.int32).contiguous()
+            rows = ops.moe_tile_rows(x.dtype, T * top, E, H, F)
+            sp, pp, tiles = ops.moe_align(ids, E, rows)
+            act = ops.moe_grouped_gemm(x, sp, top, wgu[0], tiles, T * top, True, rows)
+            us1 = timed(lambda: [ops.moe_grouped_gemm(x, sp, top, w, tiles, T * top, True, rows) for w in wgu])
+            us2 = timed(lambda: [ops.moe_grouped_gemm(act, None, 1, w, tiles, T * top, False, rows) for w in wd])
+            touched = int(torch.unique(ids).numel())
+            fl = 2 * T * top * 3 * F * H
+            by = touched * 3 * F * H * 2
+            # the dense products of equal work: an intermediate size of top * F
+            I2 = top * F
+            w1 = weights(2 * I2, H)
+            w2 = weights(H, I2)
+            xi = torch.randn(T, I2, device=dev).to(torch.bfloat16)
+            if T <= 16:
+                d1 = timed(lambda: [ops.skinny_gemm(x, w, silu_mul=True) for w in w1])
+                d2 = timed(lambda: [ops.skinny_gemm(xi, w) for w in w2])
+            else:
+                d1 = timed(lambda: [ops.silu_mul(torch.mm(x, w.t()), interleaved=True) for w in w1])
+                d2 = timed(lambda: [torch.mm(xi, w.t()) for w in w2])
+            dby = 3 * I2 * H * 2
+            out(f"routed experts T{T} ({E} x {F}, top {top}, tiles of {rows})", us1 + us2, gate_up_us=round(us1, 2),
+                down_us=round(us2, 2), GBs=round(by / (us1 + us2) / 1e3, 1), TFLOPs=round(fl / (us1 + us2) / 1e6, 1),
+                frac_hbm=round(by / (us1 + us2) / 1e3 / pk["hbm_gbs"], 3),
+                frac_flops=round(fl / (us1 + us2) / 1e6 / pk["bf16_tflops"], 3),
+                dense_us=round(d1 + d2, 2), dense_GBs=round(dby / (d1 + d2) / 1e3, 1),
+                dense_TFLOPs=round(fl / (d1 + d2) / 1e6, 1), dense_frac_hbm=round(dby / (d1 + d2) / 1e3 / pk["hbm_gbs"], 3),
+                dense_frac_flops=round(fl / (d1 + d2) / 1e6 / pk["bf16_tflops"], 3))
     return 0
 
 
@@ -507,11 +676,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels"],
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar"],
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
-                         "kernels: the hot kernels one by one")
+                         "kernels: the hot kernels one by one; dizatar: prefill and decode of the Dizatar design at "
+                         "layer sizes of real models beside the dense model of equal width")
+    ap.add_argument("--sizes", default="", help="--mode dizatar: comma-separated subset of w1024, w2048")
     ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
-                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives")
+                    "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives, latent_attention, moe")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="--mode prefill: prompt length")
     ap.add_argument("--context", type=int, default=CONTEXT, help="--mode decode: tokens each request holds")
@@ -528,6 +699,8 @@ def main():
     args.warmup = max(3, args.warmup)
     if args.mode == "kernels":
         return run_kernels(args)
+    if args.mode == "dizatar":
+        return run_dizatar(args)
     return run_ours(args)
 
 
