@@ -21,23 +21,17 @@
 #define LAT_THREADS 128
 #define LAT_MAX_ACC 8            // output numbers per thread of the general kernel: R <= 8 * 128
 
-// Rotation of pairs (i, i + dims/2), i < dims/2, by the angle pos * freq[i], angle and functions in 32-bit;
-// numbers from `dims` on pass unchanged.  src and dst hold n numbers.
+// Rotation of pairs (i, i + dims/2), i < dims/2, by the angle pos * freq[i]; cs holds cos | sin of the dims/2
+// angles (32-bit, computed once per token); numbers from `dims` on pass unchanged.  src and dst hold n numbers.
 template <typename A, typename B>
 __device__ __forceinline__ void rotate_pairs(const A* __restrict__ src, B* __restrict__ dst, int n, int dims,
-                                             const float* __restrict__ freq, float pos) {
+                                             const float* __restrict__ cs) {
     const int half = dims >> 1;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float v;
-        if (i < half) {
-            const float a = pos * freq[i];
-            v = to_f32(src[i]) * cosf(a) - to_f32(src[i + half]) * sinf(a);
-        } else if (i < dims) {
-            const float a = pos * freq[i - half];
-            v = to_f32(src[i]) * cosf(a) + to_f32(src[i - half]) * sinf(a);
-        } else {
-            v = to_f32(src[i]);
-        }
+        if (i < half) v = to_f32(src[i]) * cs[i] - to_f32(src[i + half]) * cs[half + i];
+        else if (i < dims) v = to_f32(src[i]) * cs[i - half] + to_f32(src[i - half]) * cs[i];
+        else v = to_f32(src[i]);
         dst[i] = from_f32<B>(v);
     }
 }
@@ -51,14 +45,29 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
                                          const int* __restrict__ positions, const int* __restrict__ slots,
                                          int H, int dn, int dr, int R) {
     __shared__ float scratch[33];
+    extern __shared__ float cs[];                    // cos | sin of the token's rot_dims / 2 angles
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
     const float pos = (float)positions[t];
     const A* row = proj + (size_t)t * ld;
     const int D = R + dr;
-    for (int h = 0; h < H; ++h)
-        rotate_pairs(row + (size_t)h * (dn + dr) + dn, qa + ((size_t)t * H + h) * D + R, dr, rot_dims, freq, pos);
+    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {
+        const float a = pos * freq[i];
+        cs[i] = cosf(a);
+        cs[(rot_dims >> 1) + i] = sinf(a);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < H * dr; i += blockDim.x) {     // all heads' rotated parts at once
+        const int h = i / dr, j = i - h * dr;
+        const A* src = row + (size_t)h * (dn + dr) + dn;
+        const int half = rot_dims >> 1;
+        float v;
+        if (j < half) v = to_f32(src[j]) * cs[j] - to_f32(src[j + half]) * cs[half + j];
+        else if (j < rot_dims) v = to_f32(src[j]) * cs[j - half] + to_f32(src[j - half]) * cs[j];
+        else v = to_f32(src[j]);
+        qa[((size_t)t * H + h) * D + R + j] = from_f32<A>(v);
+    }
     const int slot = slots ? slots[t] : -1;
     if (slot < 0) return;
     const A* lat = row + kv_off;
@@ -68,7 +77,7 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
     const float inv = rsqrtf(ss / (float)R + eps);
     A* dst = cache + (size_t)slot * D;
     for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<A>(to_f32(lat[i]) * inv * norm_w[i]);
-    rotate_pairs(lat + R, dst + R, dr, rot_dims, freq, pos);
+    rotate_pairs(lat + R, dst + R, dr, rot_dims, cs);
 }
 
 extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* qa, void* cache, int dtype,
@@ -76,13 +85,14 @@ extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* 
                                     const int* positions, const int* slots, int T, int H, int dn, int dr, int R,
                                     void* stream) {
     if (T <= 0) return 0;
-    if (rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || R < 1 || H < 1) return RG_ERR_UNSUPPORTED;
+    if (rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || R < 1 || H < 1 || rot_dims > 8192) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    const size_t cs_bytes = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
     if (dtype == RG_DTYPE_BF16)
-        return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(LAT_THREADS), 0, s, 1, (const bf16*)proj, ld,
+        return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const bf16*)proj, ld,
                          kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R);
     if (dtype == RG_DTYPE_F32)
-        return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(LAT_THREADS), 0, s, 1, (const float*)proj, ld,
+        return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const float*)proj, ld,
                          kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R);
     return RG_ERR_UNSUPPORTED;
 }

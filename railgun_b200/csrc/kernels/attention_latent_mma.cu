@@ -9,12 +9,14 @@
 // cache row once.
 //
 // A block works on up to 64 rows: `tt` consecutive tokens of one request x `nh` heads, in row groups of 16.
-// Each row group has TWO warps.  For a tile of 32 keys, warp c of the pair computes the scores of keys
-// [16 c, 16 c + 16) (the long product over D), the two exchange their row maxima and the bfloat16
-// weights P through shared memory (two barriers of 64 threads), and then warp c accumulates
-// O[:, its half of the R columns] += P V over all 32 keys.  Neither product is done twice, and a thread
-// holds R/4 accumulators instead of R/2.  Softmax in 32-bit in the log2 domain, running maximum and sum
-// per row; key tiles arrive through a two-stage cp.async ring, rows gathered through the block table.
+// Each row group has CW warps (2 for prompts, 4 for single tokens with up to 32 heads).  For a tile of 32
+// keys, warp c of the group computes the scores of 32 / CW keys (the long product over D, on two
+// accumulator sets so that consecutive products do not wait for each other), the warps exchange their row
+// maxima and the bfloat16 weights P through shared memory (two barriers of the group's threads), and then
+// warp c accumulates O[:, its share of the R columns] += P V over all 32 keys.  Neither product is done
+// twice, and a thread holds R / (2 CW) accumulators instead of R/2.  Softmax in 32-bit in the log2 domain,
+// running maximum and sum per row; key tiles arrive through a two-stage cp.async ring, rows gathered through
+// the block table.
 //
 // With `nsplit` > 1 (single tokens with long contexts) block z takes a contiguous share of the key tiles and
 // writes an unnormalised partial result with its maximum and sum; latent_merge adds the shares.
@@ -25,8 +27,8 @@ using namespace rgmma;
 #define LM_PAD 8                     // bf16 of padding per shared-memory row (conflict-free ldmatrix)
 #define LM_PSTRIDE (LM_BN + 8)       // row stride of the exchanged weights
 
-// NDH: 8-column tiles of the output per warp at most (R <= 16 NDH)
-template <int NDH>
+// NDH: 8-column tiles of the output per warp at most (R <= 8 NDH CW); CW: warps per row group
+template <int NDH, int CW>
 __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
         const bf16* __restrict__ qa, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
         const bf16* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
@@ -34,13 +36,16 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
         const int* __restrict__ req_of_token, const int* __restrict__ positions, int H, int hc, int R, int D,
         int page_size, int window, float scale_log2, int nsplit) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    const int RW = blockDim.x >> 6;                                // row groups of 16
+    constexpr int GT = 32 * CW;                                    // threads of a row group
+    constexpr int KW = LM_BN / CW;                                 // keys a warp scores per tile: 16 or 8
+    constexpr int NJ = KW / 8;
+    const int RW = blockDim.x / GT;                                // row groups of 16
     const int stride = D + LM_PAD;
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);                  // [16 RW][stride]
     bf16* sK = sQ + 16 * RW * stride;                              // 2 stages x [LM_BN][stride]
     bf16* sP = sK + 2 * LM_BN * stride;                            // [RW][16][LM_PSTRIDE]
-    float* sM = reinterpret_cast<float*>(sP + RW * 16 * LM_PSTRIDE);   // [RW][2][16] row maxima of a warp's keys
-    float* sL = sM + RW * 32;                                      // [RW][2][16] row sums, at the end
+    float* sM = reinterpret_cast<float*>(sP + RW * 16 * LM_PSTRIDE);   // [RW][CW][16] row maxima of a warp's keys
+    float* sL = sM + RW * CW * 16;                                 // [RW][CW][16] row sums, at the end
     pdl_wait();
     pdl_trigger();
 
@@ -64,7 +69,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
     const int kt0 = kt_first + (int)blockIdx.z * per, kt1 = min(kt_last, kt0 + per - 1);
     const int* bt = block_table + (size_t)req * max_blocks;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int rw = warp >> 1, cw = warp & 1;
+    const int rw = warp / CW, cw = warp % CW;
     const int g = lane >> 2, tq = lane & 3;
     const int lr0 = rw * 16 + g, lr1 = lr0 + 8;
     const bool ok0 = lr0 < nrows, ok1 = lr1 < nrows;
@@ -102,13 +107,13 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
     const int pos0 = ok0 ? p0 + lr0 / nh : -1, pos1 = ok1 ? p0 + lr1 / nh : -1;
     const bool warp_has_rows = rw * 16 < nrows;
     const int wfirst = p0 + (rw * 16) / nh, wlast = p0 + min(rw * 16 + 15, nrows - 1) / nh;
-    const int csplit = ((R >> 4) + 1) / 2 * 16;                    // columns [0, csplit) to warp 0, the rest to warp 1
-    const int c0 = cw ? csplit : 0, nd2 = (cw ? R - csplit : csplit) >> 4;
+    const int per16 = ((R >> 4) + CW - 1) / CW;                    // groups of 16 output columns per warp
+    const int c0 = cw * per16 * 16, nd2 = max(0, min(per16, (R >> 4) - cw * per16));
     const int a_row = (lane & 7) + ((lane >> 3) & 1) * 8, a_col = (lane >> 4) * 8;
     const int b_key = (lane & 7) + (lane >> 4) * 8, b_dim = ((lane >> 3) & 1) * 8;
     const int v_key = (lane & 7) + ((lane >> 3) & 1) * 8, v_dim = (lane >> 4) * 8;
     bf16* sPw = sP + rw * 16 * LM_PSTRIDE;
-    float* sMw = sM + rw * 32;
+    float* sMw = sM + rw * CW * 16;
     const int d16 = D >> 4;
 
     float o[NDH][4];
@@ -130,23 +135,47 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
         const int key_base = kt * LM_BN;
         const bool skip = !warp_has_rows || key_base > wlast || (window > 0 && key_base + LM_BN - 1 < wfirst - window + 1);
         if (!skip) {                                               // the same for both warps of a row group
-            float s[2][4];
+            float s[NJ][4], s2[NJ][4];
 #pragma unroll
-            for (int j = 0; j < 2; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
-#pragma unroll 4
-            for (int kd = 0; kd < d16; ++kd) {
-                uint32_t a[4], b[4];
-                ldmatrix_x4(a, sQ + (rw * 16 + a_row) * stride + kd * 16 + a_col);
-                ldmatrix_x4(b, sKs + (cw * 16 + b_key) * stride + kd * 16 + b_dim);
-                mma_bf16(s[0], a, b[0], b[1]);
-                mma_bf16(s[1], a, b[2], b[3]);
+            for (int j = 0; j < NJ; ++j) {
+                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+                s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
             }
+            const bf16* qrow = sQ + (rw * 16 + a_row) * stride + a_col;
+            const bf16* krow = CW == 2 ? sKs + (cw * KW + b_key) * stride + b_dim
+                                       : sKs + (cw * KW + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
+#pragma unroll 2
+            for (int kd = 0; kd < d16; kd += 2) {
+                uint32_t a[4], b[4];
+                ldmatrix_x4(a, qrow + kd * 16);
+                if (CW == 2) {
+                    ldmatrix_x4(b, krow + kd * 16);
+                    mma_bf16(s[0], a, b[0], b[1]);
+                    mma_bf16(s[NJ - 1], a, b[2], b[3]);
+                } else {
+                    ldmatrix_x2(b, krow + kd * 16);
+                    mma_bf16(s[0], a, b[0], b[1]);
+                }
+                if (kd + 1 < d16) {
+                    ldmatrix_x4(a, qrow + kd * 16 + 16);
+                    if (CW == 2) {
+                        ldmatrix_x4(b, krow + kd * 16 + 16);
+                        mma_bf16(s2[0], a, b[0], b[1]);
+                        mma_bf16(s2[NJ - 1], a, b[2], b[3]);
+                    } else {
+                        ldmatrix_x2(b, krow + kd * 16 + 16);
+                        mma_bf16(s2[0], a, b[0], b[1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < NJ; ++j) { s[j][0] += s2[j][0]; s[j][1] += s2[j][1]; s[j][2] += s2[j][2]; s[j][3] += s2[j][3]; }
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < NJ; ++j) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const int key = key_base + cw * 16 + j * 8 + tq * 2 + (e & 1);
+                    const int key = key_base + cw * KW + j * 8 + tq * 2 + (e & 1);
                     const int prow = e < 2 ? pos0 : pos1;
                     float v = s[j][e] * scale_log2;
                     if (!(key <= prow && (window <= 0 || key > prow - window))) v = -INFINITY;
@@ -159,22 +188,25 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
             mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
             if (tq == 0) { sMw[cw * 16 + g] = mx0; sMw[cw * 16 + g + 8] = mx1; }
-            pair_barrier(1 + rw);
-            mx0 = fmaxf(mx0, sMw[(cw ^ 1) * 16 + g]);
-            mx1 = fmaxf(mx1, sMw[(cw ^ 1) * 16 + g + 8]);
+            group_barrier<GT>(1 + rw);
+#pragma unroll
+            for (int c = 0; c < CW; ++c) {
+                mx0 = fmaxf(mx0, sMw[c * 16 + g]);
+                mx1 = fmaxf(mx1, sMw[c * 16 + g + 8]);
+            }
             const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
             const float ms0 = mn0 == -INFINITY ? 0.f : mn0, ms1 = mn1 == -INFINITY ? 0.f : mn1;
             const float al0 = ex2(m0 - ms0), al1 = ex2(m1 - ms1);
             m0 = mn0; m1 = mn1;
             float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
+            for (int j = 0; j < NJ; ++j) {
                 s[j][0] = ex2(s[j][0] - ms0); s[j][1] = ex2(s[j][1] - ms0);
                 s[j][2] = ex2(s[j][2] - ms1); s[j][3] = ex2(s[j][3] - ms1);
                 rs0 += s[j][0] + s[j][1];
                 rs1 += s[j][2] + s[j][3];
-                *reinterpret_cast<uint32_t*>(sPw + g * LM_PSTRIDE + cw * 16 + j * 8 + tq * 2) = pack_bf16(s[j][0], s[j][1]);
-                *reinterpret_cast<uint32_t*>(sPw + (g + 8) * LM_PSTRIDE + cw * 16 + j * 8 + tq * 2) = pack_bf16(s[j][2], s[j][3]);
+                *reinterpret_cast<uint32_t*>(sPw + g * LM_PSTRIDE + cw * KW + j * 8 + tq * 2) = pack_bf16(s[j][0], s[j][1]);
+                *reinterpret_cast<uint32_t*>(sPw + (g + 8) * LM_PSTRIDE + cw * KW + j * 8 + tq * 2) = pack_bf16(s[j][2], s[j][3]);
             }
             l0 = l0 * al0 + rs0;                                   // this thread's keys only; added up at the end
             l1 = l1 * al1 + rs1;
@@ -182,7 +214,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
 #pragma unroll
                 for (int i = 0; i < NDH; ++i) { o[i][0] *= al0; o[i][1] *= al0; o[i][2] *= al1; o[i][3] *= al1; }
             }
-            pair_barrier(1 + rw);
+            group_barrier<GT>(1 + rw);
 #pragma unroll
             for (int kk = 0; kk < LM_BN / 16; ++kk) {
                 uint32_t a[4];
@@ -203,11 +235,12 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
     if (!warp_has_rows) return;
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
     l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    float* sLw = sL + rw * 32;
+    float* sLw = sL + rw * CW * 16;
     if (tq == 0) { sLw[cw * 16 + g] = l0; sLw[cw * 16 + g + 8] = l1; }
-    pair_barrier(1 + rw);
-    l0 += sLw[(cw ^ 1) * 16 + g];
-    l1 += sLw[(cw ^ 1) * 16 + g + 8];
+    group_barrier<GT>(1 + rw);
+    l0 = l1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CW; ++c) { l0 += sLw[c * 16 + g]; l1 += sLw[c * 16 + g + 8]; }
     if (nsplit == 1) {
         const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
         bf16* o0 = out + ((size_t)tok0 * H + hd0) * R + c0;
@@ -242,24 +275,33 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
                                     bf16* __restrict__ out, const int* __restrict__ rows_list, int H, int R, int nsplit) {
     pdl_wait();
     pdl_trigger();
+    extern __shared__ float wz[];                  // a share's factor 2^(m_z - M) / L, 0 for a share without keys
     const int t = rows_list ? rows_list[blockIdx.x] : blockIdx.x, h = blockIdx.y;
     const size_t base = ((size_t)t * H + h) * nsplit;
-    float M = -INFINITY;
-    for (int z = 0; z < nsplit; ++z)
-        if (part_ml[(base + z) * 2 + 1] > 0.f) M = fmaxf(M, part_ml[(base + z) * 2]);
-    float L = 0.f;
-    for (int z = 0; z < nsplit; ++z) {
-        const float l = part_ml[(base + z) * 2 + 1];
-        if (l > 0.f) L += l * ex2(part_ml[(base + z) * 2] - M);
+    if (threadIdx.x < 32) {
+        float M = -INFINITY;
+        for (int z = threadIdx.x; z < nsplit; z += 32)
+            if (part_ml[(base + z) * 2 + 1] > 0.f) M = fmaxf(M, part_ml[(base + z) * 2]);
+        M = warp_max(M);
+        float L = 0.f;
+        for (int z = threadIdx.x; z < nsplit; z += 32) {
+            const float l = part_ml[(base + z) * 2 + 1];
+            const float f = l > 0.f ? ex2(part_ml[(base + z) * 2] - M) : 0.f;
+            wz[z] = f;
+            L += l * f;
+        }
+        L = warp_sum(L);
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        for (int z = threadIdx.x; z < nsplit; z += 32) wz[z] *= inv;
     }
-    const float inv = L > 0.f ? 1.f / L : 0.f;
+    __syncthreads();
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
         float acc = 0.f;
         for (int z = 0; z < nsplit; ++z) {
-            if (part_ml[(base + z) * 2 + 1] > 0.f)
-                acc += part_o[(base + z) * R + c] * ex2(part_ml[(base + z) * 2] - M);
+            const float f = wz[z];
+            if (f > 0.f) acc += part_o[(base + z) * R + c] * f;
         }
-        out[((size_t)t * H + h) * R + c] = __float2bfloat16_rn(acc * inv);
+        out[((size_t)t * H + h) * R + c] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -268,7 +310,7 @@ template <typename K> static int lm_allow_smem(K kernel, size_t bytes) {
 }
 
 static size_t lm_smem_bytes(int RW, int D) {
-    return (size_t)(16 * RW + 2 * LM_BN) * (D + LM_PAD) * 2 + (size_t)RW * 16 * LM_PSTRIDE * 2 + (size_t)RW * 64 * 4;
+    return (size_t)(16 * RW + 2 * LM_BN) * (D + LM_PAD) * 2 + (size_t)RW * 16 * LM_PSTRIDE * 2 + (size_t)RW * 128 * 4;
 }
 
 // Whether the sizes fit these kernels (0: yes).
@@ -301,17 +343,19 @@ extern "C" int rg_latent_attention_mma(
         if (nsplit > 1 && (!part_o || !part_ml)) return RG_ERR_UNSUPPORTED;
     }
     const size_t smem = lm_smem_bytes(RW, D);
-    const int ndh = ((R >> 4) + 1) / 2 * 2;
-    dim3 grid(n_items * sub, chunks, nsplit), block(64 * RW);
+    const int CW = (!tiles && RW <= 2) ? 4 : 2;                    // single tokens of up to 32 heads: four warps per row group
+    const int ndh = ((R >> 4) + CW - 1) / CW * 2;
+    dim3 grid(n_items * sub, chunks, nsplit), block(32 * CW * RW);
     const float scale_log2 = scale * 1.4426950408889634f;
     int e;
-#define RG_LM(N) { e = lm_allow_smem(latent_attention_mma_kernel<N>, smem); if (e) return e; \
-        e = rg_launch(latent_attention_mma_kernel<N>, grid, block, smem, s, 1, (const bf16*)qa, (bf16*)out, part_o, part_ml, \
+#define RG_LM(N, C) { e = lm_allow_smem(latent_attention_mma_kernel<N, C>, smem); if (e) return e; \
+        e = rg_launch(latent_attention_mma_kernel<N, C>, grid, block, smem, s, 1, (const bf16*)qa, (bf16*)out, part_o, part_ml, \
                       (const bf16*)cache, block_table, max_blocks, tiles, sub, tt, rows_list, req_of_token, positions, H, hc, \
                       R, D, page_size, window, scale_log2, nsplit); }
-    if (ndh <= 8) RG_LM(8) else if (ndh <= 16) RG_LM(16) else RG_LM(32)
+    if (CW == 2) { if (ndh <= 8) RG_LM(8, 2) else if (ndh <= 16) RG_LM(16, 2) else RG_LM(32, 2) }
+    else { if (ndh <= 4) RG_LM(4, 4) else if (ndh <= 8) RG_LM(8, 4) else RG_LM(16, 4) }
 #undef RG_LM
     if (e || nsplit == 1) return e;
-    return rg_launch(latent_merge_kernel, dim3(n_items, H), dim3(R >= 256 ? 128 : 64), 0, s, 1, (const float*)part_o,
+    return rg_launch(latent_merge_kernel, dim3(n_items, H), dim3(R >= 256 ? 128 : 64), (size_t)nsplit * sizeof(float), s, 1, (const float*)part_o,
                      (const float*)part_ml, (bf16*)out, rows_list, H, R, nsplit);
 }

@@ -78,10 +78,16 @@ __device__ __forceinline__ void store_chunk(const uint32_t (&v)[32], OUT* __rest
 // Persistent: CTA b works on tiles b, b + gridDim.x, ... (rows of C fastest, so that CTAs running at the same
 // time share a tile of B in L2).  Two accumulators in TMEM: while the epilogue warps drain one, the MMA warp
 // fills the other.
-template <int BN, int STAGES, int EPI, typename OUT>
+//
+// GROUPED: the rows of A belong to groups (experts), each with its own B.  `gtiles` lists the row tiles,
+// [g_mtiles][3] = (group or -1 for an unused entry, first row, rows <= 128); B holds the groups' matrices one
+// after the other, `rows_b` rows each.  A tile's box of 128 rows may reach into the next group's rows or past the
+// end of A (zeros): those rows are computed and not stored.
+template <int BN, int STAGES, int EPI, typename OUT, bool GROUPED = false>
 __global__ void __launch_bounds__(TC_THREADS)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               OUT* __restrict__ out, int ldo, int M, int N, int K, int* err) {
+               OUT* __restrict__ out, int ldo, int M, int N, int K, int* err,
+               const int* __restrict__ gtiles = nullptr, int g_mtiles = 0, int rows_b = 0) {
     extern __shared__ unsigned char smem_raw[];
     constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
     const uint32_t base = (smem_addr(smem_raw) + 1023u) & ~1023u;          // swizzled tiles need 1024-byte alignment
@@ -95,7 +101,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KT = (K + TC_BK - 1) / TC_BK;
-    const int m_tiles = (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const int m_tiles = GROUPED ? g_mtiles : (M + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
     const int total_tiles = m_tiles * n_tiles;
     constexpr uint32_t TMEM_COLS = 2 * BN;                                  // 256 or 512: a power of two
 
@@ -118,14 +124,22 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-            const int m0 = (t % m_tiles) * TC_BM, n0 = (t / m_tiles) * BN;
+            int m0 = (t % m_tiles) * TC_BM;
+            const int n0 = (t / m_tiles) * BN;
+            int brow = n0;
+            if (GROUPED) {
+                const int* tl = gtiles + 3 * (t % m_tiles);
+                if (tl[0] < 0) continue;                                    // every role skips the same entries
+                m0 = tl[1];
+                brow = tl[0] * rows_b + n0;
+            }
             for (int kt = 0; kt < KT; ++kt, ++it) {
                 const int s = it % STAGES, r = it / STAGES;
                 if (r > 0 && !mbar_wait(empty_bar(s), (r & 1) ^ 1, err, 1, &abort_flag)) { ok = false; break; }
                 mbar_expect_tx(full_bar(s), STAGE_BYTES);
                 const uint32_t sa = base + s * STAGE_BYTES;
                 tma_load_2d(sa, &map_a, full_bar(s), kt * TC_BK, m0);
-                tma_load_2d(sa + A_BYTES, &map_b, full_bar(s), kt * TC_BK, n0);
+                tma_load_2d(sa + A_BYTES, &map_b, full_bar(s), kt * TC_BK, brow);
             }
         }
     } else if (warp == 5 && lane == 0) {
@@ -134,6 +148,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int it = 0, local = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+            if (GROUPED && gtiles[3 * (t % m_tiles)] < 0) { --local; continue; }
             const int b = local & 1, u = local >> 1;
             if (u > 0 && !mbar_wait(acc_empty(b), (u & 1) ^ 1, err, 4, &abort_flag)) { ok = false; break; }
             tc_fence_after();
@@ -156,10 +171,17 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         int local = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+            if (GROUPED && gtiles[3 * (t % m_tiles)] < 0) { --local; continue; }
             const int b = local & 1, u = local >> 1;
             if (!mbar_wait(acc_full(b), u & 1, err, 3, &abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const int m0 = (t % m_tiles) * TC_BM, n0 = (t / m_tiles) * BN;
+            int m0 = (t % m_tiles) * TC_BM, row_end = M;
+            const int n0 = (t / m_tiles) * BN;
+            if (GROUPED) {
+                const int* tl = gtiles + 3 * (t % m_tiles);
+                m0 = tl[1];
+                row_end = min(M, tl[1] + tl[2]);
+            }
             const int row = m0 + warp * 32 + lane;
             const uint32_t tmem_d = tmem_base + (uint32_t)(b * BN) + ((uint32_t)(warp * 32) << 16);
 #pragma unroll 1
@@ -167,7 +189,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 uint32_t v[32];
                 tc_ld32(tmem_d + (uint32_t)(c * 32), v);
                 const int col0 = n0 + c * 32;
-                if (row < M && col0 < N) store_chunk<EPI, OUT>(v, out, ldo, row, col0, N);
+                if (row < row_end && col0 < N) store_chunk<EPI, OUT>(v, out, ldo, row, col0, N);
             }
             tc_fence_before();
             __syncwarp();
@@ -207,7 +229,7 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, OUT* out, int
     const int num_sms = rg_num_sms();
     const int tiles = ((N + BN - 1) / BN) * ((M + TC_BM - 1) / TC_BM);
     dim3 grid(tiles < num_sms ? tiles : num_sms);                          // persistent: one CTA per SM at most
-    return rg_launch(kernel, grid, dim3(TC_THREADS), smem, s, 1, ma, mb, out, ldo, M, N, K, err);
+    return rg_launch(kernel, grid, dim3(TC_THREADS), smem, s, 1, ma, mb, out, ldo, M, N, K, err, (const int*)nullptr, 0, 0);
 }
 
 // ---- the same product on CTA pairs: tiles of 256 x BN, one pair per two SMs (cta_group::2) ----------------
@@ -384,4 +406,28 @@ extern "C" int rg_tc_gemm(const void* A, int lda, const void* B, void* out, int 
         return wide ? launch_tc<256, 4, EPI_NONE, float>(ma, mb, (float*)out, ldo, M, N, K, err, s)
                     : launch_tc<128, 6, EPI_NONE, float>(ma, mb, (float*)out, ldo, M, N, K, err, s);
     return RG_ERR_UNSUPPORTED;
+}
+
+
+// The grouped product: rows of A [M, K] in group order, `tiles` [max_tiles][3] = (group or -1, first row, rows <= 128),
+// B [groups * N, K] (every group's N rows one after the other), out [M, N] bfloat16.  Same conditions as rg_tc_gemm.
+extern "C" int rg_tc_gemm_grouped(const void* A, int lda, int M, const void* B, int groups, int N, int K, void* out,
+                                  int ldo, const int* tiles, int max_tiles, int* err, void* stream) {
+    if (M <= 0 || N <= 0 || max_tiles <= 0) return 0;
+    if (K <= 0 || K % 8 || lda % 8 || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || groups < 1) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    constexpr int BN = 256, STAGES = 4;
+    CUtensorMap ma, mb;
+    int e = rg_make_map(&ma, A, M, K, lda, TC_BM);
+    if (e) return e;
+    e = rg_make_map(&mb, B, (unsigned long long)groups * N, K, K, BN);
+    if (e) return e;
+    const size_t smem = (size_t)STAGES * (TC_BM * TC_BK * 2 + BN * TC_BK * 2) + 8 * (2 * STAGES + 4) + 1024;
+    auto kernel = tc_gemm_kernel<BN, STAGES, EPI_NONE, bf16, true>;
+    cudaError_t ce = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (ce != cudaSuccess) return (int)ce;
+    const int num_sms = rg_num_sms();
+    const long long total = (long long)max_tiles * ((N + BN - 1) / BN);
+    dim3 grid((unsigned)(total < num_sms ? total : num_sms));
+    return rg_launch(kernel, grid, dim3(TC_THREADS), smem, s, 1, ma, mb, (bf16*)out, ldo, M, N, K, err, tiles, max_tiles, N);
 }

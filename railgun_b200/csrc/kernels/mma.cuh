@@ -40,14 +40,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
-// A barrier among the 64 threads of two warps that name the same `id` (1..4; 0 is __syncthreads).  The id is
-// an immediate in every branch so that the kernel reserves five barriers, not all sixteen.
-__device__ __forceinline__ void pair_barrier(int id) {
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];\n" : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
+// A barrier among the THREADS threads (whole warps) that name the same `id` (1..4; 0 is __syncthreads).  The
+// id is an immediate in every branch so that the kernel reserves five barriers, not all sixteen.
+template <int THREADS>
+__device__ __forceinline__ void group_barrier(int id) {
     switch (id) {
-        case 1: asm volatile("bar.sync 1, 64;\n" ::: "memory"); break;
-        case 2: asm volatile("bar.sync 2, 64;\n" ::: "memory"); break;
-        case 3: asm volatile("bar.sync 3, 64;\n" ::: "memory"); break;
-        default: asm volatile("bar.sync 4, 64;\n" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 1, %0;\n" ::"n"(THREADS) : "memory"); break;
+        case 2: asm volatile("bar.sync 2, %0;\n" ::"n"(THREADS) : "memory"); break;
+        case 3: asm volatile("bar.sync 3, %0;\n" ::"n"(THREADS) : "memory"); break;
+        default: asm volatile("bar.sync 4, %0;\n" ::"n"(THREADS) : "memory"); break;
     }
 }
 

@@ -11,13 +11,12 @@
 // the products run over a list of row tiles that `moe_align` writes (at most pairs / tile + E of them; the
 // launch covers that bound and unused tiles return at once), which keeps a step capturable in a CUDA graph.
 //
-//   moe_route          one block per four tokens: its warps share the router's rows, then take a token each
+//   moe_route          one block per four tokens: its warps (up to 32) share the router's rows, then take a token each
 //   moe_align          one block: counts per expert, segment starts, the pairs in expert order, the tile list
 //   moe_grouped_gemm   32-bit arithmetic on CUDA cores, any sizes and both storage types (the true 32-bit path)
 //   moe_combine        one block per token, 32-bit sum in the order of the choices
 #include "common.cuh"
 
-#define ROUTE_WARPS 4
 #define ROUTE_TOKENS 4        // tokens per block: a router row is read once for all of them
 
 template <typename A>
@@ -27,20 +26,41 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
     extern __shared__ float sm[];                 // per token of the block: N scores, N choice scores
     pdl_wait();
     pdl_trigger();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
     const int t0 = blockIdx.x * ROUTE_TOKENS;
     const int nt = min(ROUTE_TOKENS, T - t0);
     float* base = sm;
-    for (int n = warp; n < N; n += ROUTE_WARPS) {
+    // every lane adds its own elements in index order (four at a time where rows start on 16-byte boundaries),
+    // then the lanes are added up: a token's logits do not depend on what else is in the step
+    const bool vec = (W & 3) == 0 && sizeof(A) == 2;
+    for (int n = warp; n < N; n += nwarps) {
         const float* wr = router + (size_t)n * W;
         float dot[ROUTE_TOKENS];
 #pragma unroll
         for (int j = 0; j < ROUTE_TOKENS; ++j) dot[j] = 0.f;
-        for (int i = lane; i < W; i += 32) {
-            const float r = wr[i];
+        if (vec) {
+            for (int i = lane * 4; i < W; i += 128) {
+                const float4 r = *reinterpret_cast<const float4*>(wr + i);
 #pragma unroll
-            for (int j = 0; j < ROUTE_TOKENS; ++j)
-                if (j < nt) dot[j] += r * to_f32(x[(size_t)(t0 + j) * W + i]);
+                for (int j = 0; j < ROUTE_TOKENS; ++j) {
+                    if (j < nt) {
+                        const uint2 raw = *reinterpret_cast<const uint2*>(x + (size_t)(t0 + j) * W + i);
+                        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+                        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+                        dot[j] += r.x * __low2float(lo);
+                        dot[j] += r.y * __high2float(lo);
+                        dot[j] += r.z * __low2float(hi);
+                        dot[j] += r.w * __high2float(hi);
+                    }
+                }
+            }
+        } else {
+            for (int i = lane; i < W; i += 32) {
+                const float r = wr[i];
+#pragma unroll
+                for (int j = 0; j < ROUTE_TOKENS; ++j)
+                    if (j < nt) dot[j] += r * to_f32(x[(size_t)(t0 + j) * W + i]);
+            }
         }
 #pragma unroll
         for (int j = 0; j < ROUTE_TOKENS; ++j) {
@@ -49,7 +69,7 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
         }
     }
     __syncthreads();
-    for (int j = warp; j < nt; j += ROUTE_WARPS) {
+    for (int j = warp; j < nt; j += nwarps) {
         const int t = t0 + j;
         float* s = base + (size_t)j * 2 * N;
         float* c = s + N;
@@ -97,7 +117,8 @@ extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const
     const size_t smem = (size_t)ROUTE_TOKENS * 2 * N * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(ROUTE_WARPS * 32);
+    const int warps = N < 4 ? 4 : (N > 32 ? 32 : N);               // a warp per router row, up to 32
+    dim3 grid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS), block(warps * 32);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(moe_route_kernel<bf16>, grid, block, smem, s, 1, (const bf16*)x, router, correction, ids,
                          weights, T, W, N, top);
@@ -268,14 +289,22 @@ __global__ void moe_combine_kernel(const A* __restrict__ x, const A* __restrict_
                                    const int* __restrict__ pair_pos, float* __restrict__ out, int W, int E, int top) {
     pdl_wait();
     pdl_trigger();
+    extern __shared__ float csm[];                 // per choice: weight, row of y (-1: the token's own row)
     const int t = blockIdx.x;
+    float* cw = csm;
+    int* crow = reinterpret_cast<int*>(csm + top);
+    for (int k = threadIdx.x; k < top; k += blockDim.x) {
+        const size_t p = (size_t)t * top + k;
+        cw[k] = weights[p];
+        crow[k] = ids[p] < E ? pair_pos[p] : -1;
+    }
+    __syncthreads();
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         float v = 0.f;
+        const float own = to_f32(x[(size_t)t * W + i]);
         for (int k = 0; k < top; ++k) {
-            const size_t p = (size_t)t * top + k;
-            const int e = ids[p];
-            const float g = weights[p];
-            v += g * (e < E ? to_f32(y[(size_t)pair_pos[p] * W + i]) : to_f32(x[(size_t)t * W + i]));
+            const int row = crow[k];
+            v += cw[k] * (row >= 0 ? to_f32(y[(size_t)row * W + i]) : own);
         }
         if (shared) v += to_f32(shared[(size_t)t * W + i]);
         out[(size_t)t * W + i] = v;
@@ -288,11 +317,13 @@ extern "C" int rg_moe_combine(const void* x, const void* y, const void* shared, 
     if (T <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = W >= 1024 ? 256 : 128;
+    const size_t csmem = (size_t)top * 8;
+    if (top < 1 || csmem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     if (dtype == RG_DTYPE_BF16)
-        return rg_launch(moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, s, 1, (const bf16*)x, (const bf16*)y,
+        return rg_launch(moe_combine_kernel<bf16>, dim3(T), dim3(threads), csmem, s, 1, (const bf16*)x, (const bf16*)y,
                          (const bf16*)shared, ids, weights, pair_pos, out, W, E, top);
     if (dtype == RG_DTYPE_F32)
-        return rg_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, s, 1, (const float*)x, (const float*)y,
+        return rg_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), csmem, s, 1, (const float*)x, (const float*)y,
                          (const float*)shared, ids, weights, pair_pos, out, W, E, top);
     return RG_ERR_UNSUPPORTED;
 }

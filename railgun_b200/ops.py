@@ -268,7 +268,7 @@ def latent_attention_mma_ok(dtype, H: int, R: int, D: int) -> bool:
     of at most 512 numbers, a row that fits shared memory."""
     if dtype != torch.bfloat16 or R % 16 or D % 16 or not 16 <= R <= 512 or D < R:
         return False
-    return (64 + 64) * (D + 8) * 2 + 4 * 16 * 40 * 2 + 4 * 64 * 4 <= 227 * 1024
+    return (64 + 64) * (D + 8) * 2 + 4 * 16 * 40 * 2 + 4 * 128 * 4 <= 227 * 1024
 
 
 def latent_decode_splits(n_tokens: int, head_chunks: int, max_context: int) -> int:
