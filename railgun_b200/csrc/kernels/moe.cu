@@ -129,7 +129,7 @@ extern "C" int rg_moe_route(const void* x, int dtype, const float* router, const
 }
 
 // ids: [P] chosen router outputs of the P = T * top pairs.  Pairs whose output is >= E (identity experts) get
-// no place.  sorted_pair[pos] = pair at place pos; pair_pos[pair] = its place or -1; tiles[i] = (expert, first
+// no place.  sorted_pair[pos] = pair at place pos (-1 for the places left over); pair_pos[pair] = its place or -1; tiles[i] = (expert, first
 // place, places) in tiles of `tile_rows`, expert -1 for the unused tail of the list (max_tiles entries).
 __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int tile_rows, int* __restrict__ sorted_pair,
                                  int* __restrict__ pair_pos, int* __restrict__ tiles, int max_tiles) {
@@ -177,6 +177,7 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int P, int E, int 
             tl[2] = min(tile_rows, count[e] - i * tile_rows);
         }
     }
+    for (int pos = start[E] + threadIdx.x; pos < P; pos += blockDim.x) sorted_pair[pos] = -1;   // places nobody has
     for (int i = tstart[E] + threadIdx.x; i < max_tiles; i += blockDim.x) {
         tiles[3 * (size_t)i] = -1;
         tiles[3 * (size_t)i + 1] = 0;
@@ -328,12 +329,34 @@ extern "C" int rg_moe_combine(const void* x, const void* y, const void* shared, 
     return RG_ERR_UNSUPPORTED;
 }
 
+// out[pos] = a[src[pos] / src_div] for every place that has a pair (rows of K bfloat16 numbers, K % 8 == 0, copied
+// 16 bytes at a time): the experts' input in expert order, for a product that reads its rows through TMA.
+__global__ void moe_gather_rows_kernel(const bf16* __restrict__ a, int lda, const int* __restrict__ src, int src_div,
+                                       bf16* __restrict__ out, int K) {
+    pdl_wait();
+    pdl_trigger();
+    const int pos = blockIdx.x;
+    const int pair = src[pos];
+    if (pair < 0) return;
+    const uint4* from = reinterpret_cast<const uint4*>(a + (size_t)(pair / src_div) * lda);
+    uint4* to = reinterpret_cast<uint4*>(out + (size_t)pos * K);
+    for (int i = threadIdx.x; i < (K >> 3); i += blockDim.x) to[i] = from[i];
+}
+
+extern "C" int rg_moe_gather_rows(const void* a, int lda, const int* src, int src_div, void* out, int P, int K,
+                                  void* stream) {
+    if (P <= 0) return 0;
+    if ((K & 7) || (lda & 7) || src_div < 1 || (((uintptr_t)a | (uintptr_t)out) & 15)) return RG_ERR_UNSUPPORTED;
+    return rg_launch(moe_gather_rows_kernel, dim3(P), dim3(K >= 2048 ? 256 : 128), 0, (cudaStream_t)stream, 1,
+                     (const bf16*)a, lda, src, src_div, (bf16*)out, K);
+}
+
 // ---------------------------------------------------------------------------------------------------
 // The same product on the tensor cores (bfloat16, mma.sync m16n8k16, 32-bit accumulators): one block per
 // (tile of BM places of one expert, 64 output columns), the expert's rows W[n0 .. n0 + 64) and the tile's
 // gathered input rows streamed through a three-stage cp.async ring in steps of 64 along K.  With few places
 // per expert (decode) the block is a weight-streaming product whose tile is mostly padding; with many
-// (prompts) BM = 128 places share every weight row that is read.  GATED: gate and up rows side by side,
+// (prompts) the products go to the tcgen05 kernel instead (gemm_tcgen05.cu, grouped).  GATED: gate and up rows side by side,
 // silu(gate) * up in the epilogue, in 32-bit.  K and lda must be multiples of 8 (16-byte copies).
 #include "mma.cuh"
 
@@ -458,12 +481,12 @@ template <typename KF> static int gm_allow_smem(KF kernel, size_t bytes) {
     return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-// tile_rows: 32 or 128, the tile size `moe_align` was given.
+// tile_rows: 32, the tile size `moe_align` was given.
 extern "C" int rg_moe_grouped_gemm_mma(const void* a, int lda, const int* src, int src_div, const void* w, void* out,
                                        int ldo, const int* tiles, int max_tiles, int tile_rows, int N, int K,
                                        int gated, void* stream) {
     if (max_tiles <= 0 || N <= 0) return 0;
-    if ((tile_rows != 32 && tile_rows != 128) || K < 8 || (K & 7) || (lda & 7) || src_div < 1) return RG_ERR_UNSUPPORTED;
+    if (tile_rows != 32 || K < 8 || (K & 7) || (lda & 7) || src_div < 1) return RG_ERR_UNSUPPORTED;
     if (((uintptr_t)a | (uintptr_t)w) & 15) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(max_tiles, (N + GM_BN - 1) / GM_BN);
@@ -472,9 +495,7 @@ extern "C" int rg_moe_grouped_gemm_mma(const void* a, int lda, const int* src, i
         e = gm_allow_smem(moe_grouped_gemm_mma_kernel<BM, G>, smem); if (e) return e; \
         return rg_launch(moe_grouped_gemm_mma_kernel<BM, G>, grid, dim3(BM == 128 ? 256 : 128), smem, s, 1, \
                          (const bf16*)a, lda, src, src_div, (const bf16*)w, (bf16*)out, ldo, tiles, N, K); }
-    if (tile_rows == 32 && gated) RG_GM(32, true)
-    if (tile_rows == 32 && !gated) RG_GM(32, false)
-    if (tile_rows == 128 && gated) RG_GM(128, true)
-    RG_GM(128, false)
+    if (gated) RG_GM(32, true)
+    RG_GM(32, false)
 #undef RG_GM
 }

@@ -354,8 +354,9 @@ def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles:
     out = silu(gate) * up).  Row ``pos`` of the input is ``a[src[pos] // src_div]``
     or, without ``src``, ``a[pos]``.  Returns [places, N]; rows that belong to no
     tile are not written.  bfloat16 with rows on 16-byte boundaries runs on the
-    tensor cores (tiles of 32 or 128 places), everything else in 32-bit
-    arithmetic on the CUDA cores (tiles of 32)."""
+    tensor cores (tiles of 32 places: mma.sync, weight-streaming; tiles of 128:
+    the grouped tcgen05 product, whose bounded waits ``tc_gemm_check`` reports
+    on), everything else in 32-bit arithmetic on the CUDA cores (tiles of 32)."""
     _check(a, "a")
     _check(w, "w", a.dtype)
     _check(tiles, "tiles", torch.int32)
@@ -365,6 +366,28 @@ def moe_grouped_gemm(a: torch.Tensor, src, src_div: int, w: torch.Tensor, tiles:
     N = rows_w // 2 if gated else rows_w
     if a.shape[1] != K or (gated and rows_w % 2):
         raise KernelError(f"moe_grouped_gemm: a {tuple(a.shape)} vs w {tuple(w.shape)}")
+    if tile_rows == 128:
+        if not moe_grouped_gemm_tc_ok(a.dtype, K, a.stride(0)):
+            raise KernelError("moe_grouped_gemm: tiles of 128 places are for the tensor-core path")
+        # prompts: the tcgen05 product over the tile list (its rows come through TMA, so they are gathered
+        # into expert order first); gate and up as one product, silu * up by the activation kernel
+        if src is not None:
+            rows = torch.empty((places, K), dtype=a.dtype, device=a.device)
+            _ok(_fn("moe", "rg_moe_gather_rows")(_ptr(a), c_int(a.stride(0)), _ptr(src), c_int(src_div), _ptr(rows),
+                                                 c_int(places), c_int(K), _stream()), "moe_gather_rows")
+            a = rows
+        elif a.shape[0] != places:
+            raise KernelError(f"moe_grouped_gemm: {a.shape[0]} rows for {places} places")
+        err = _tc_err.get(a.device)
+        if err is None:
+            err = _tc_err[a.device] = torch.zeros(1, dtype=torch.int32, device=a.device)
+        global _tc_unchecked
+        _tc_unchecked = True
+        wide = torch.empty((places, rows_w), dtype=a.dtype, device=a.device)
+        _ok(_fn("gemm_tcgen05", "rg_tc_gemm_grouped")(
+            _ptr(a), c_int(a.stride(0)), c_int(places), _ptr(w), c_int(E), c_int(rows_w), c_int(K), _ptr(wide),
+            c_int(rows_w), _ptr(tiles), c_int(tiles.shape[0]), _ptr(err), _stream()), "tc_gemm_grouped")
+        return silu_mul(wide) if gated else wide
     out = torch.empty((places, N), dtype=a.dtype, device=a.device)
     if moe_grouped_gemm_tc_ok(a.dtype, K, a.stride(0)):
         _ok(_fn("moe", "rg_moe_grouped_gemm_mma")(
@@ -385,7 +408,7 @@ def moe_grouped_gemm_tc_ok(dtype, K: int, lda: int) -> bool:
 
 
 def moe_tile_rows(dtype, pairs: int, num_experts: int, K1: int, K2: int) -> int:
-    """Places per tile of the grouped products: 128 on the tensor cores once an expert gets 64 places on
+    """Places per tile of the grouped products: 128 (the tcgen05 product) once an expert gets 64 places on
     average (prompts: every weight row that is read serves 128 rows), else 32."""
     tc = moe_grouped_gemm_tc_ok(dtype, K1, K1) and moe_grouped_gemm_tc_ok(dtype, K2, K2)
     return 128 if tc and pairs >= 64 * max(1, num_experts) else MOE_TILE_ROWS
