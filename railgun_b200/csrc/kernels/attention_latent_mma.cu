@@ -10,7 +10,7 @@
 //
 // A block works on up to 64 rows: `tt` consecutive tokens of one request x `nh` heads, in row groups of 16.
 // Each row group has CW warps (2 for prompts, 4 for single tokens with up to 32 heads).  For a tile of 32
-// keys, warp c of the group computes the scores of 32 / CW keys (the long product over D, on two
+// keys, warp c of the group computes the scores of 32 / CW keys (the long product over D, on two or four
 // accumulator sets so that consecutive products do not wait for each other), the warps exchange their row
 // maxima and the bfloat16 weights P through shared memory (two barriers of the group's threads), and then
 // warp c accumulates O[:, its share of the R columns] += P V over all 32 keys.  Neither product is done
@@ -92,13 +92,20 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
     }
     // a key row is copied by blockDim.x / 32 threads, 16 bytes at a time; keys beyond `hi` are zeros
     const int tpk = blockDim.x >> 5, my_key = tid / tpk, my_c0 = tid - my_key * tpk;
+    // the page of this thread's key row is looked up one tile ahead, so that the table read is off the
+    // critical path when the copies are issued
+    auto page_of = [&](int kt) {
+        const int key = kt * LM_BN + my_key;
+        return key <= hi ? bt[key / page_size] : -1;
+    };
+    int page_next = page_of(kt0);
     auto load_keys = [&](int kt, bf16* dst) {
         const int key = kt * LM_BN + my_key;
-        const bool valid = key <= hi;
-        const bf16* src = cache;
-        if (valid) src = cache + ((size_t)bt[key / page_size] * page_size + key % page_size) * D;
+        const bool valid = page_next >= 0;
+        const bf16* src = valid ? cache + ((size_t)page_next * page_size + key % page_size) * D : cache;
         bf16* d = dst + my_key * stride;
         for (int c = my_c0; c < chunks; c += tpk) cp_async16(d + c * 8, src + c * 8, valid);
+        page_next = page_of(kt + 1);
     };
     load_keys(kt0, sK);
     cp_async_commit();
@@ -135,41 +142,47 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
         const int key_base = kt * LM_BN;
         const bool skip = !warp_has_rows || key_base > wlast || (window > 0 && key_base + LM_BN - 1 < wfirst - window + 1);
         if (!skip) {                                               // the same for both warps of a row group
-            float s[NJ][4], s2[NJ][4];
+            // NCH accumulator sets take the steps over D in turn, so that consecutive products do not wait for
+            // each other and the fragment loads of several steps are in flight together
+            constexpr int NCH = CW == 4 ? 4 : 2;
+            float sc[NCH][NJ][4];
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) {
-                s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
-                s2[j][0] = s2[j][1] = s2[j][2] = s2[j][3] = 0.f;
-            }
+            for (int c = 0; c < NCH; ++c)
+#pragma unroll
+                for (int j = 0; j < NJ; ++j) { sc[c][j][0] = sc[c][j][1] = sc[c][j][2] = sc[c][j][3] = 0.f; }
             const bf16* qrow = sQ + (rw * 16 + a_row) * stride + a_col;
             const bf16* krow = CW == 2 ? sKs + (cw * KW + b_key) * stride + b_dim
                                        : sKs + (cw * KW + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
-#pragma unroll 2
-            for (int kd = 0; kd < d16; kd += 2) {
-                uint32_t a[4], b[4];
-                ldmatrix_x4(a, qrow + kd * 16);
-                if (CW == 2) {
-                    ldmatrix_x4(b, krow + kd * 16);
-                    mma_bf16(s[0], a, b[0], b[1]);
-                    mma_bf16(s[NJ - 1], a, b[2], b[3]);
-                } else {
-                    ldmatrix_x2(b, krow + kd * 16);
-                    mma_bf16(s[0], a, b[0], b[1]);
+#pragma unroll 1
+            for (int kd = 0; kd < d16; kd += NCH) {
+                uint32_t a[NCH][4], b[NCH][4];
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    if (kd + c < d16) {
+                        ldmatrix_x4(a[c], qrow + (kd + c) * 16);
+                        if (CW == 2) ldmatrix_x4(b[c], krow + (kd + c) * 16);
+                        else ldmatrix_x2(b[c], krow + (kd + c) * 16);
+                    }
                 }
-                if (kd + 1 < d16) {
-                    ldmatrix_x4(a, qrow + kd * 16 + 16);
-                    if (CW == 2) {
-                        ldmatrix_x4(b, krow + kd * 16 + 16);
-                        mma_bf16(s2[0], a, b[0], b[1]);
-                        mma_bf16(s2[NJ - 1], a, b[2], b[3]);
-                    } else {
-                        ldmatrix_x2(b, krow + kd * 16 + 16);
-                        mma_bf16(s2[0], a, b[0], b[1]);
+#pragma unroll
+                for (int c = 0; c < NCH; ++c) {
+                    if (kd + c < d16) {
+                        mma_bf16(sc[c][0], a[c], b[c][0], b[c][1]);
+                        if (CW == 2) mma_bf16(sc[c][NJ - 1], a[c], b[c][2], b[c][3]);
                     }
                 }
             }
+            float s[NJ][4];
 #pragma unroll
-            for (int j = 0; j < NJ; ++j) { s[j][0] += s2[j][0]; s[j][1] += s2[j][1]; s[j][2] += s2[j][2]; s[j][3] += s2[j][3]; }
+            for (int j = 0; j < NJ; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float v = sc[0][j][e];
+#pragma unroll
+                    for (int c = 1; c < NCH; ++c) v += sc[c][j][e];
+                    s[j][e] = v;
+                }
+            }
             float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
             for (int j = 0; j < NJ; ++j) {

@@ -273,9 +273,9 @@ def latent_attention_mma_ok(dtype, H: int, R: int, D: int) -> bool:
 
 def latent_decode_splits(n_tokens: int, head_chunks: int, max_context: int) -> int:
     """How many shares a single token's context is cut into: enough blocks to fill the device twice, at least
-    128 keys a share."""
+    64 keys a share."""
     by_residency = 296 // max(1, n_tokens * head_chunks)
-    by_length = -(-max_context // 128)
+    by_length = -(-max_context // 64)
     return max(1, min(by_residency, by_length, 64))
 
 

@@ -408,3 +408,92 @@ def test_command_line_and_trace_runner(tmp_path):
     got2 = np.fromfile(tmp_path / "2.f32", dtype="<f4").reshape(1, 211)
     assert not (tmp_path / "1.f32").exists()
     assert np.abs(got0 - ref[[0, 18]]).max() < 1e-4 and np.abs(got2[0] - ref[29]).max() < 1e-4
+
+
+# ---- the attention kernels and the re-injection alone ---------------------------------------------------
+
+def plain_latent_rows(qa, rows, pos, R, scale, window=0):
+    """One token's heads over its request's cache rows [0, pos]: scores over the whole row, values its first R."""
+    lo = max(0, pos - window + 1) if window else 0
+    keys = rows[lo:pos + 1]
+    p = torch.softmax((qa @ keys.T) * scale, dim=-1)
+    return p @ keys[:, :R]
+
+
+@pytest.mark.parametrize("H,R,dr,page,window", [(5, 16, 16, 4, 0), (16, 512, 64, 16, 0), (70, 48, 16, 8, 0),
+                                                (40, 96, 32, 32, 0), (3, 32, 0, 1, 0), (8, 64, 16, 16, 37)])
+def test_latent_attention_kernels_alone(H, R, dr, page, window):
+    """Both attention kernels over hand-made cache rows behind a shuffled block table: a portion of a prompt (a
+    tile of 64 positions and one of 6) beside a single token of another request, and single tokens alone with
+    their contexts cut into one, three and seven shares; more heads than a block takes, one head chunk, a latent
+    of 512, a window."""
+    from railgun_b200 import ops
+    g = torch.Generator().manual_seed(H * 1000 + R)
+    D, ctx = R + dr, (200, 77)
+    n_pages = [-(-c // page) for c in ctx]
+    perm = torch.randperm(sum(n_pages) + 3, generator=g)
+    table = torch.zeros((2, max(n_pages)), dtype=torch.int32)
+    table[0, :n_pages[0]] = perm[:n_pages[0]]
+    table[1, :n_pages[1]] = perm[n_pages[0]:n_pages[0] + n_pages[1]]
+    rows = [torch.randn(c, D, generator=g).to(torch.bfloat16) for c in ctx]
+    cache = torch.zeros((sum(n_pages) + 3, page, D), dtype=torch.bfloat16)
+    for r in range(2):
+        for j in range(ctx[r]):
+            cache[table[r, j // page], j % page] = rows[r][j]
+    scale = 1.7 / D ** 0.5
+    # rows 0..69: request 0 at positions 130..199; row 70: request 1 at position 76
+    positions = torch.tensor(list(range(130, 200)) + [76], dtype=torch.int32)
+    req = torch.tensor([0] * 70 + [1], dtype=torch.int32)
+    qa = torch.randn(71, H, D, generator=g).to(torch.bfloat16)
+    ref = torch.stack([plain_latent_rows(qa[t].double(), rows[int(req[t])].double(), int(positions[t]), R, scale, window)
+                       for t in range(71)])
+    dev = lambda t: t.to(DEV)
+    got = ops.latent_attention_general(dev(qa), dev(cache), dev(table), dev(req), dev(positions), R, window, scale)
+    assert rel(got, ref) < 8e-3
+    assert ops.latent_attention_mma_ok(torch.bfloat16, H, R, D)
+    out = torch.zeros((71, H, R), dtype=torch.bfloat16, device=DEV)
+    tiles = torch.tensor([[0, 64, 0], [64, 6, 0]], dtype=torch.int32)
+    ops.latent_attention_mma(dev(qa), out, dev(cache), dev(table), dev(tiles), None, 2, dev(req), dev(positions), R,
+                             window, scale)
+    ops.latent_attention_mma(dev(qa), out, dev(cache), dev(table), None, dev(torch.tensor([70], dtype=torch.int32)), 1,
+                             dev(req), dev(positions), R, window, scale, 2)
+    assert rel(out, ref) < 8e-3
+    # single tokens only: three requests' last positions, rows 0..2
+    pos1 = torch.tensor([199, 76, 150], dtype=torch.int32)
+    req1 = torch.tensor([0, 1, 0], dtype=torch.int32)
+    ref1 = torch.stack([plain_latent_rows(qa[t].double(), rows[int(req1[t])].double(), int(pos1[t]), R, scale, window)
+                        for t in range(3)])
+    for splits in (1, 3, 7):
+        out1 = torch.zeros((3, H, R), dtype=torch.bfloat16, device=DEV)
+        ops.latent_attention_mma(dev(qa[:3].contiguous()), out1, dev(cache), dev(table), None, None, 3, dev(req1),
+                                 dev(pos1), R, window, scale, splits)
+        assert rel(out1, ref1) < 8e-3, f"{splits} shares"
+    assert not ops.latent_attention_mma_ok(torch.bfloat16, H, 40, 48) and not ops.latent_attention_mma_ok(torch.float32, H, R, D)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_reinjection_alone(dtype):
+    """x <- W [x + pending; x0] with x0 the stream at the start of the step."""
+    from railgun_b200 import ops
+    from railgun_b200.parts.base import Stream
+    from railgun_b200.parts.registry import STREAM_OPS
+    rng = np.random.default_rng(5)
+    Hd, T, dt = 40, 9, TORCH[dtype]
+    t = {"loop.in": torch.tensor(rng.normal(size=(Hd, 2 * Hd)) * 0.2)}
+    part = STREAM_OPS.get("reinject")(dict(hidden_size=Hd, name="loop.in"), "", env_of(dt, Hd), bank_of(t, dt))
+    x0 = torch.tensor(rng.normal(size=(T, Hd)), dtype=torch.float32)
+    moved = torch.tensor(rng.normal(size=(T, Hd)), dtype=torch.float32)
+    y = torch.tensor(rng.normal(size=(T, Hd)), dtype=torch.float32).to(dt)
+    wb = torch.tensor(1 + 0.2 * rng.normal(size=Hd), dtype=torch.float32)
+    stream = Stream(x0.clone().to(DEV))
+    part.begin(stream, None)
+    stream.resid = moved.clone().to(DEV)                       # layers ran in between
+    stream.pending = ops.PendingNormed(y.to(DEV), wb.to(DEV), 1e-5)
+    part.apply(stream, None)
+    w = rounded(t, dt)["loop.in"]
+    x = moved.double() + P.rms_norm(y.double(), wb.double(), 1e-5)
+    both = torch.cat([x, x0.double()], dim=-1)
+    if dt == torch.bfloat16:
+        both = both.to(torch.bfloat16).double()
+    assert stream.pending is None and stream.resid.dtype == torch.float32
+    assert rel(stream.resid, both @ w.T) < (1e-5 if dtype == "float32" else 2e-2)
