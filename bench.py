@@ -406,6 +406,54 @@ def dizatar_sizes(name):
     raise ValueError(name)
 
 
+def dizatar_runs(cfg):
+    """The layers in the order they run (a looped span ``times`` times)."""
+    n, loop = len(cfg["layers"]), cfg.get("loop")
+    if not loop:
+        return list(range(n)), 0
+    order = list(range(loop["start"])) + list(range(loop["start"], loop["stop"])) * loop["times"] + list(range(loop["stop"], n))
+    return order, loop["times"]
+
+
+def dizatar_decode_bytes(cfg, batch, context):
+    """Bytes a decode step of ``batch`` tokens has to read: attention and shared-expert weights once per layer run,
+    the experts that the batch is expected to touch under uniform routing, the head, and the latent cache."""
+    W, V = cfg["width"], cfg["vocab"]
+    order, passes = dizatar_runs(cfg)
+    total = V * W * 2 + passes * 2 * W * W * 2
+    for i in order:
+        m, f = cfg["layers"][i]["mixer"], cfg["layers"][i]["mlp"]
+        H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        total += (H * (dn + dr) * W + (R + dr) * W + H * dn * R + H * dv * R + W * H * dv) * 2
+        total += batch * context * (R + dr) * 2
+        if f:
+            E, ident, top, F = f["router"]["experts"], f["router"]["identity"], f["router"]["top"], f["expert"]["ff"]
+            touched = E * (1.0 - (1.0 - top / (E + ident)) ** batch)
+            total += touched * 3 * F * W * 2 + (E + ident) * W * 4
+            if f.get("shared"):
+                total += 3 * f["shared"]["ff"] * W * 2
+    return total
+
+
+def dizatar_prefill_flops(cfg, T):
+    """FLOPs of one prompt of T tokens as the engine computes it (attention in the absorbed form: scores over
+    latent + rotated numbers, values over the latent)."""
+    W, V = cfg["width"], cfg["vocab"]
+    order, passes = dizatar_runs(cfg)
+    total = 2 * V * W + passes * 2 * T * 2 * W * W
+    for i in order:
+        m, f = cfg["layers"][i]["mixer"], cfg["layers"][i]["mlp"]
+        H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+        total += 2 * T * (H * (dn + dr) * W + (R + dr) * W + H * dn * R + H * dv * R + W * H * dv)
+        total += H * 2 * (2 * R + dr) * (T * (T + 1) // 2)
+        if f:
+            E, ident, top, F = f["router"]["experts"], f["router"]["identity"], f["router"]["top"], f["expert"]["ff"]
+            total += 2 * T * (top * E / (E + ident) * 3 * F * W + (E + ident) * W)
+            if f.get("shared"):
+                total += 2 * T * 3 * f["shared"]["ff"] * W
+    return total
+
+
 def run_dizatar(args):
     """Prefill and decode throughput of Dizatar at layer sizes of real models (random weights), beside the dense
     GQA Llama of equal width, number of layer runs and vocabulary.  One JSON line per model and size."""
@@ -414,6 +462,7 @@ def run_dizatar(args):
     from railgun_b200.engine.batch import StepEntry
     from railgun_b200.engine.engine import Engine
     page, pool_tokens = 16, 64 * 4096
+    pk, pk_src = peaks()
     for size in (args.sizes.split(",") if args.sizes else ["w1024", "w2048"]):
         for label, cfg in zip(("dizatar", "llama"), dizatar_sizes(size)):
             mdir = model_folder(cfg)
@@ -429,6 +478,11 @@ def run_dizatar(args):
                 tok_s, ms, n_launch, _ = time_decode(b, args.steps, args.warmup, 1000 * b, args.context)
                 line[f"decode_b{b}_tok_s"], line[f"decode_b{b}_ms"] = round(tok_s, 1), round(ms, 4)
                 line[f"decode_b{b}_launches_per_step"] = n_launch // args.steps
+                ctx = args.context + args.warmup + args.steps // 2
+                by = (dizatar_decode_bytes(cfg, b, ctx) if label == "dizatar"
+                      else decode_bytes(cfg, b, ctx, runner.cache.bytes_per_token()))
+                line[f"decode_b{b}_GB_per_step"] = round(by / 1e9, 3)
+                line[f"decode_b{b}_frac_hbm"] = round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
             prompt = rng.integers(0, V, size=args.tokens).tolist()
             times = []
             for i in range(args.warmup + 7):
@@ -442,7 +496,10 @@ def run_dizatar(args):
                 times.append(t0.elapsed_time(t1))
             runner.check_device_errors()
             ms = sorted(times[args.warmup:])[len(times[args.warmup:]) // 2]
-            line.update(prefill_tokens=args.tokens, prefill_ms=round(ms, 3), prefill_tok_s=round(args.tokens / ms * 1e3, 1))
+            fl = dizatar_prefill_flops(cfg, args.tokens) if label == "dizatar" else prefill_flops(cfg, args.tokens)
+            line.update(prefill_tokens=args.tokens, prefill_ms=round(ms, 3), prefill_tok_s=round(args.tokens / ms * 1e3, 1),
+                        prefill_TFLOP=round(fl / 1e12, 3), prefill_frac_flops=round(fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                        peaks=pk_src)
             print(json.dumps(line), flush=True)
             del eng, runner, time_decode
             torch.cuda.empty_cache()

@@ -43,9 +43,10 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
                                          A* __restrict__ cache, const float* __restrict__ norm_w, float eps,
                                          const float* __restrict__ freq, int rot_dims,
                                          const int* __restrict__ positions, const int* __restrict__ slots,
-                                         int H, int dn, int dr, int R) {
+                                         int H, int dn, int dr, int R, A* __restrict__ q_back) {
     __shared__ float scratch[33];
-    extern __shared__ float cs[];                    // cos | sin of the token's rot_dims / 2 angles
+    extern __shared__ float cs[];                    // cos | sin of the token's rot_dims / 2 angles; then H * dr rotated numbers
+    float* rot_q = cs + rot_dims;
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
@@ -66,7 +67,15 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
         if (j < half) v = to_f32(src[j]) * cs[j] - to_f32(src[j + half]) * cs[half + j];
         else if (j < rot_dims) v = to_f32(src[j]) * cs[j - half] + to_f32(src[j - half]) * cs[j];
         else v = to_f32(src[j]);
-        qa[((size_t)t * H + h) * D + R + j] = from_f32<A>(v);
+        if (qa) qa[((size_t)t * H + h) * D + R + j] = from_f32<A>(v);
+        if (q_back) rot_q[i] = v;
+    }
+    if (q_back) {                                    // in place: every partner has been read before anything is written
+        __syncthreads();
+        for (int i = threadIdx.x; i < H * dr; i += blockDim.x) {
+            const int h = i / dr, j = i - h * dr;
+            q_back[(size_t)t * ld + (size_t)h * (dn + dr) + dn + j] = from_f32<A>(rot_q[i]);
+        }
     }
     const int slot = slots ? slots[t] : -1;
     if (slot < 0) return;
@@ -80,20 +89,24 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
     rotate_pairs(lat + R, dst + R, dr, rot_dims, cs);
 }
 
+// q_in_place: the rotated query parts also replace the unrotated ones in proj (qa may then be null).
 extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* qa, void* cache, int dtype,
                                     const float* norm_w, float eps, const float* freq, int rot_dims,
                                     const int* positions, const int* slots, int T, int H, int dn, int dr, int R,
-                                    void* stream) {
+                                    int q_in_place, void* stream) {
     if (T <= 0) return 0;
     if (rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || R < 1 || H < 1 || rot_dims > 8192) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t cs_bytes = (size_t)(rot_dims > 0 ? rot_dims : 1) * sizeof(float);
+    const size_t cs_bytes = (size_t)((rot_dims > 0 ? rot_dims : 1) + (q_in_place ? H * dr : 0)) * sizeof(float);
+    if (cs_bytes > 48 * 1024) return RG_ERR_UNSUPPORTED;
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const bf16*)proj, ld,
-                         kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R);
+                         kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R,
+                         q_in_place ? (bf16*)proj : (bf16*)nullptr);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const float*)proj, ld,
-                         kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R);
+                         kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R,
+                         q_in_place ? (float*)proj : (float*)nullptr);
     return RG_ERR_UNSUPPORTED;
 }
 
@@ -180,5 +193,100 @@ extern "C" int rg_latent_attention_general(
         return rg_launch(latent_attention_general_kernel<float>, grid, dim3(LAT_THREADS), smem, s, 1,
                          (const float*)qa, (float*)out, (const float*)cache, block_table, max_blocks, req_of_token,
                          positions, H, R, D, page_size, window, scale);
+    return RG_ERR_UNSUPPORTED;
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Prompts in the expanded form.  For a request that brings several tokens, a head's keys [U_k c | k_r] and
+// values U_v c are cheaper to attend to than the compressed rows (dn + dr + dv numbers per key and head instead
+// of 2 R + dr), so the step expands the request's context once: latent_gather copies the context's latent
+// vectors into a dense matrix (a library product then applies U_k and U_v to all of them), and latent_pack_kv
+// lays the result out as ordinary key/value pages [pages, 2, H, page, d], d = dn + dr (values zero-padded from
+// dv to d), which the dense model's flash kernel reads.  The temporary pages are numbered request by request:
+// page j of the step's request r is page r * max_blocks + j.  Requests that bring one token are skipped.
+
+// lat [requests * max_blocks * page_size, R]: row (r * max_blocks + j) * page_size + o = latent of r's token j * page_size + o
+template <typename A>
+__global__ void latent_gather_kernel(const A* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
+                                     const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                                     A* __restrict__ lat, int page_size, int R, int D) {
+    pdl_wait();
+    pdl_trigger();
+    const int j = blockIdx.x, r = blockIdx.y;
+    if (cu_seqlens[r + 1] - cu_seqlens[r] < 2) return;
+    const int ctx = context_lens[r];
+    if (j * page_size >= ctx) return;
+    const int page = block_table[(size_t)r * max_blocks + j];
+    if (page < 0) return;
+    const int n = min(page_size, ctx - j * page_size);
+    const A* src = cache + (size_t)page * page_size * D;
+    A* dst = lat + ((size_t)r * max_blocks + j) * page_size * R;
+    for (int i = threadIdx.x; i < n * R; i += blockDim.x) {
+        const int o = i / R, c = i - o * R;
+        dst[(size_t)o * R + c] = src[(size_t)o * D + c];
+    }
+}
+
+extern "C" int rg_latent_gather(const void* cache, const int* block_table, int max_blocks, const int* cu_seqlens,
+                                const int* context_lens, void* lat, int dtype, int requests, int page_size, int R, int D,
+                                void* stream) {
+    if (requests <= 0 || max_blocks <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(max_blocks, requests);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(latent_gather_kernel<bf16>, grid, dim3(256), 0, s, 1, (const bf16*)cache, block_table, max_blocks,
+                         cu_seqlens, context_lens, (bf16*)lat, page_size, R, D);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(latent_gather_kernel<float>, grid, dim3(256), 0, s, 1, (const float*)cache, block_table,
+                         max_blocks, cu_seqlens, context_lens, (float*)lat, page_size, R, D);
+    return RG_ERR_UNSUPPORTED;
+}
+
+// kn [N, H * dn], vv [N, H * dv] (rows as in lat), the rotated key parts from the cache rows' last dr numbers
+// -> kv [requests * max_blocks, 2, H, page_size, d]
+template <typename A>
+__global__ void latent_pack_kv_kernel(const A* __restrict__ kn, const A* __restrict__ vv, const A* __restrict__ cache,
+                                      const int* __restrict__ block_table, int max_blocks,
+                                      const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                                      A* __restrict__ kv, int page_size, int H, int dn, int dr, int dv, int R) {
+    pdl_wait();
+    pdl_trigger();
+    const int j = blockIdx.x, r = blockIdx.y;
+    if (cu_seqlens[r + 1] - cu_seqlens[r] < 2) return;
+    const int ctx = context_lens[r];
+    if (j * page_size >= ctx) return;
+    const int page = block_table[(size_t)r * max_blocks + j];
+    if (page < 0) return;
+    const int n = min(page_size, ctx - j * page_size);
+    const int d = dn + dr, D = R + dr;
+    const size_t tp = (size_t)r * max_blocks + j;                  // the temporary page
+    A* kdst = kv + tp * 2 * H * page_size * d;
+    A* vdst = kdst + (size_t)H * page_size * d;
+    const size_t row0 = tp * page_size;
+    const A* krot = cache + (size_t)page * page_size * D + R;
+    for (int i = threadIdx.x; i < H * n * d; i += blockDim.x) {
+        const int h = i / (n * d), rem = i - h * n * d, o = rem / d, c = rem - o * d;
+        kdst[((size_t)h * page_size + o) * d + c] = c < dn ? kn[(row0 + o) * H * dn + (size_t)h * dn + c]
+                                                           : krot[(size_t)o * D + c - dn];
+        vdst[((size_t)h * page_size + o) * d + c] = c < dv ? vv[(row0 + o) * H * dv + (size_t)h * dv + c] : from_f32<A>(0.f);
+    }
+}
+
+extern "C" int rg_latent_pack_kv(const void* kn, const void* vv, const void* cache, const int* block_table,
+                                 int max_blocks, const int* cu_seqlens, const int* context_lens, void* kv, int dtype,
+                                 int requests, int page_size, int H, int dn, int dr, int dv, int R, void* stream) {
+    if (requests <= 0 || max_blocks <= 0) return 0;
+    if (dv > dn + dr) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(max_blocks, requests);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(latent_pack_kv_kernel<bf16>, grid, dim3(256), 0, s, 1, (const bf16*)kn, (const bf16*)vv,
+                         (const bf16*)cache, block_table, max_blocks, cu_seqlens, context_lens, (bf16*)kv, page_size, H, dn,
+                         dr, dv, R);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(latent_pack_kv_kernel<float>, grid, dim3(256), 0, s, 1, (const float*)kn, (const float*)vv,
+                         (const float*)cache, block_table, max_blocks, cu_seqlens, context_lens, (float*)kv, page_size, H,
+                         dn, dr, dv, R);
     return RG_ERR_UNSUPPORTED;
 }

@@ -310,6 +310,7 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
     __syncthreads();
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
         float acc = 0.f;
+#pragma unroll 4
         for (int z = 0; z < nsplit; ++z) {
             const float f = wz[z];
             if (f > 0.f) acc += part_o[(base + z) * R + c] * f;

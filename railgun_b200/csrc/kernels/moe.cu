@@ -39,6 +39,7 @@ __global__ void moe_route_kernel(const A* __restrict__ x, const float* __restric
 #pragma unroll
         for (int j = 0; j < ROUTE_TOKENS; ++j) dot[j] = 0.f;
         if (vec) {
+#pragma unroll 4
             for (int i = lane * 4; i < W; i += 128) {
                 const float4 r = *reinterpret_cast<const float4*>(wr + i);
 #pragma unroll

@@ -208,26 +208,31 @@ def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
     return logits
 
 
-def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa: torch.Tensor, cache, norm_w: torch.Tensor, eps: float,
+def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa, cache, norm_w: torch.Tensor, eps: float,
                       freq: torch.Tensor, rot_dims: int, positions: torch.Tensor, slots, H: int, dn: int, dr: int,
-                      R: int) -> None:
+                      R: int, q_in_place: bool = False) -> None:
     """Per token of ``proj`` [T, H (dn + dr) + R + dr] (queries per head as
     [dn plain | dr rotated], then at ``kv_off`` the compressed key/value vector
     [R | dr]): rotate every head's rotated part into ``qa`` [T, H, R + dr][:, :, R:],
     and write [RMS norm of the R latent numbers times ``norm_w`` | rotated key
     part] into row ``slots[t]`` of ``cache`` [pages, page, R + dr] (``slots``
     None or a negative slot: no write).  Rotation: pairs (i, i + rot_dims / 2) by
-    position * ``freq[i]``, in 32-bit."""
+    position * ``freq[i]``, in 32-bit.  ``q_in_place``: the rotated parts also
+    replace the unrotated ones in ``proj`` (``qa`` may then be None)."""
     _check(proj, "proj")
-    _check(qa, "qa", proj.dtype)
+    if qa is None and not q_in_place:
+        raise KernelError("latent_rope_cache: nowhere to put the rotated query parts")
+    if qa is not None:
+        _check(qa, "qa", proj.dtype)
     _check(norm_w, "norm_w", torch.float32)
     _check(freq, "freq", torch.float32)
     _check(positions, "positions", torch.int32)
     T = proj.shape[0]
     D = R + dr
-    if proj.shape[1] < kv_off + D or kv_off < H * (dn + dr) or qa.shape != (T, H, D) or positions.numel() != T:
-        raise KernelError(f"latent_rope_cache: proj {tuple(proj.shape)}, qa {tuple(qa.shape)} do not match "
-                          f"{H} heads x ({dn} + {dr}), latent {R}")
+    if (proj.shape[1] < kv_off + D or kv_off < H * (dn + dr) or (qa is not None and qa.shape != (T, H, D))
+            or positions.numel() != T):
+        raise KernelError(f"latent_rope_cache: proj {tuple(proj.shape)}, qa {None if qa is None else tuple(qa.shape)} "
+                          f"do not match {H} heads x ({dn} + {dr}), latent {R}")
     if norm_w.numel() != R or freq.numel() < rot_dims // 2:
         raise KernelError("latent_rope_cache: norm weight or frequency table of the wrong size")
     if slots is not None:
@@ -238,7 +243,41 @@ def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa: torch.Tensor, cache, 
     _ok(_fn("attention_latent", "rg_latent_rope_cache")(
         _ptr(proj), c_int(proj.stride(0)), c_int(kv_off), _ptr(qa), _ptr(cache if slots is not None else None),
         c_int(_dtype_code(proj)), _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions),
-        _ptr(slots), c_int(T), c_int(H), c_int(dn), c_int(dr), c_int(R), _stream()), "latent_rope_cache")
+        _ptr(slots), c_int(T), c_int(H), c_int(dn), c_int(dr), c_int(R), c_int(1 if q_in_place else 0), _stream()),
+        "latent_rope_cache")
+
+
+def latent_expand_context(cache: torch.Tensor, block_table: torch.Tensor, cu_seqlens: torch.Tensor,
+                          context_lens: torch.Tensor, w_uk: torch.Tensor, w_uv: torch.Tensor, H: int, dn: int, dr: int,
+                          dv: int, R: int):
+    """The contexts of the step's requests that bring several tokens, expanded from the latent cache
+    [pages, page, R + dr] into ordinary key/value pages [requests * max_blocks, 2, H, page, dn + dr] (keys
+    [U_k c | rotated part], values U_v c zero-padded to dn + dr), numbered request by request.  Returns (pages,
+    their block table [requests, max_blocks])."""
+    _check(cache, "cache")
+    _check(block_table, "block_table", torch.int32)
+    _check(cu_seqlens, "cu_seqlens", torch.int32)
+    _check(context_lens, "context_lens", torch.int32)
+    _check(w_uk, "w_uk", cache.dtype)
+    _check(w_uv, "w_uv", cache.dtype)
+    n_req, MB = block_table.shape
+    page, D = cache.shape[1], cache.shape[2]
+    if D != R + dr or w_uk.shape != (H * dn, R) or w_uv.shape != (H * dv, R) or dv > dn + dr:
+        raise KernelError("latent_expand_context: sizes do not match")
+    N = n_req * MB * page
+    lat = torch.empty((N, R), dtype=cache.dtype, device=cache.device)
+    _ok(_fn("attention_latent", "rg_latent_gather")(
+        _ptr(cache), _ptr(block_table), c_int(MB), _ptr(cu_seqlens), _ptr(context_lens), _ptr(lat),
+        c_int(_dtype_code(cache)), c_int(n_req), c_int(page), c_int(R), c_int(D), _stream()), "latent_gather")
+    kn = linear(lat, w_uk)
+    vv = linear(lat, w_uv)
+    kv = torch.empty((n_req * MB, 2, H, page, dn + dr), dtype=cache.dtype, device=cache.device)
+    _ok(_fn("attention_latent", "rg_latent_pack_kv")(
+        _ptr(kn), _ptr(vv), _ptr(cache), _ptr(block_table), c_int(MB), _ptr(cu_seqlens), _ptr(context_lens), _ptr(kv),
+        c_int(_dtype_code(cache)), c_int(n_req), c_int(page), c_int(H), c_int(dn), c_int(dr), c_int(dv), c_int(R),
+        _stream()), "latent_pack_kv")
+    table = torch.arange(n_req * MB, dtype=torch.int32, device=cache.device).view(n_req, MB)
+    return kv, table
 
 
 def latent_attention_general(qa: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,

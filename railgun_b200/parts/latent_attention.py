@@ -87,20 +87,72 @@ class LatentAttention(Mixer):
         self.w_o = tensors.get(n["o"], env.dtype)
         self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, float(p["rot_base"])),
                                         lambda: rotary_frequencies(self.rot_dims, p["rot_base"]).to(env.device))
+        # Prompts attend in the expanded form (keys [U_k c | k_rot], values U_v c per head: dn + dr + dv numbers
+        # per key and head instead of 2 R + dr) through the dense model's flash kernel, where the sizes fit it.
+        d = self.dn + self.dr
+        self.expands_prompts = (env.dtype == torch.bfloat16 and d % 16 == 0 and 16 <= d <= 256 and self.dv <= d
+                                and self.window == 0 and d + self.dv < 2 * self.R + self.dr)
+        if self.expands_prompts:
+            self.w_uk_flat = tensors.get(n["uk"], env.dtype)                                # [H dn, R]
+            self.w_uv_flat = tensors.get(n["uv"], env.dtype)                                # [H dv, R]
+            pad = torch.zeros((self.w_o.shape[0], self.H, d), dtype=env.dtype, device=self.w_o.device)
+            pad[:, :, :self.dv] = self.w_o.view(-1, self.H, self.dv)
+            self.w_o_padded = pad.view(-1, self.H * d).contiguous()                         # zero columns behind each head's dv
 
     def forward(self, x, batch, cache, writes=True):
         H, dn, dr, dv, R, D = self.H, self.dn, self.dr, self.dv, self.R, self.D
         T = x.shape[0]
         proj = ops.linear(x, self.w_proj)                                                  # [T, H (dn + dr) + R + dr]
+        slots = batch.slot_mapping[cache.group] if writes else None
+        if self._expand_this_step(batch, cache, T):
+            return self._forward_expanded(proj, batch, cache, slots)
         qa = torch.empty((T, H, D), dtype=proj.dtype, device=proj.device)
         q_plain = proj[:, :self.kv_off].view(T, H, dn + dr)[:, :, :dn].transpose(0, 1)     # [H, T, dn], no copy
         torch.bmm(q_plain, self.w_uk, out=qa[:, :, :R].transpose(0, 1))
         ops.latent_rope_cache(proj, self.kv_off, qa, cache.kv, self.norm_w, self.eps, self.freq, self.rot_dims,
-                              batch.positions, batch.slot_mapping[cache.group] if writes else None, H, dn, dr, R)
+                              batch.positions, slots, H, dn, dr, R)
         o_lat = self.attend(qa, batch, cache)                                              # [T, H, R]
         heads = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
         torch.bmm(o_lat.transpose(0, 1), self.w_uv_t, out=heads.view(T, H, dv).transpose(0, 1))
         return ops.linear(heads, self.w_o)
+
+    def _expand_this_step(self, batch, cache, T) -> bool:
+        """Prompts go through the expanded form when the step has some and the temporary pages (every request of
+        the step at the block table's width) stay within a few times the step's tokens."""
+        if not self.expands_prompts or batch.decode_only or not batch.num_prefill_tiles:
+            return False
+        table = batch.block_table[cache.group]
+        return table.shape[0] * table.shape[1] * cache.page_size <= max(8192, 4 * T)
+
+    def _forward_expanded(self, proj, batch, cache, slots):
+        H, dn, dr, dv, R, D = self.H, self.dn, self.dr, self.dv, self.R, self.D
+        T, d = proj.shape[0], self.dn + self.dr
+        table = batch.block_table[cache.group]
+        out = torch.zeros((T, H * d), dtype=proj.dtype, device=proj.device)
+        qa = None
+        if batch.num_decode_rows:
+            # the step's single tokens stay in the compressed form; their rows of `out` are filled first
+            qa = torch.empty((T, H, D), dtype=proj.dtype, device=proj.device)
+            q_plain = proj[:, :self.kv_off].view(T, H, d)[:, :, :dn].transpose(0, 1)
+            torch.bmm(q_plain, self.w_uk, out=qa[:, :, :R].transpose(0, 1))
+        ops.latent_rope_cache(proj, self.kv_off, qa, cache.kv, self.norm_w, self.eps, self.freq, self.rot_dims,
+                              batch.positions, slots, H, dn, dr, R, q_in_place=True)
+        if batch.num_decode_rows:
+            n = batch.num_decode_rows
+            o_lat = torch.zeros((T, H, R), dtype=proj.dtype, device=proj.device)
+            if ops.latent_attention_mma_ok(qa.dtype, H, R, D):
+                ops.latent_attention_mma(qa, o_lat, cache.kv, table, None, batch.decode_rows, n, batch.req_of_token,
+                                         batch.positions, R, self.window, self.scale,
+                                         ops.latent_decode_splits(n, -(-H // 64), batch.max_context_len))
+            else:
+                o_lat = ops.latent_attention_general(qa, cache.kv, table, batch.req_of_token, batch.positions, R,
+                                                     self.window, self.scale)
+            torch.bmm(o_lat.transpose(0, 1), self.w_uv_t, out=out.view(T, H, d)[:, :, :dv].transpose(0, 1))
+        kv, kv_table = ops.latent_expand_context(cache.kv, table, batch.cu_seqlens, batch.context_lens, self.w_uk_flat,
+                                                 self.w_uv_flat, H, dn, dr, dv, R)
+        ops.prefill_attention(proj, proj.stride(0), out, kv, kv_table, batch.prefill_tiles, batch.positions, H, H, d,
+                              0, self.scale)
+        return ops.linear(out, self.w_o_padded)
 
     def attend(self, qa, batch, cache):
         """bfloat16 with sizes in steps of 16 runs on the tensor cores (requests with several tokens in tiles of

@@ -55,7 +55,16 @@ CASE_N = dict(
     layers=[layer(mixer(16, 16, 32, 16, 128, base=500000.0), moe(4, 4, 3, 32, 48)),
             layer(mixer(16, 16, 32, 16, 128, base=500000.0), None)])
 
-CASES = {"P": (CASE_P, 3, 8), "Q": (CASE_Q, 5, 16), "S": (CASE_S, 7, 4), "N": (CASE_N, 9, 32)}   # config, seed, page
+# M: six heads of 48 + 32 over a latent of 80 with values of 40 (every size a different multiple of 8), one
+#    layer looped twice and one behind it.
+CASE_M = dict(
+    architecture="Dizatar", width=72, vocab=150, norm=dict(eps=1e-5), residual_mult=0.9, logit_softcap=20.0,
+    loop=dict(start=0, stop=1, times=2),
+    layers=[layer(mixer(6, 48, 32, 40, 80, base=3000.0), moe(6, 2, 2, 40, 24)),
+            layer(mixer(6, 48, 32, 40, 80, base=3000.0), None)])
+
+CASES = {"P": (CASE_P, 3, 8), "Q": (CASE_Q, 5, 16), "S": (CASE_S, 7, 4), "N": (CASE_N, 9, 32),
+         "M": (CASE_M, 11, 16)}                                                                # config, seed, page
 
 _made: dict = {}
 _plain: dict = {}
