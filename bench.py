@@ -436,8 +436,10 @@ def dizatar_decode_bytes(cfg, batch, context):
 
 
 def dizatar_prefill_flops(cfg, T):
-    """FLOPs of one prompt of T tokens as the engine computes it (attention in the absorbed form: scores over
-    latent + rotated numbers, values over the latent)."""
+    """FLOPs of one prompt of T tokens as the engine computes it: attention in the expanded form where the
+    engine expands prompts (keys of dn + dr and values of dv numbers per head, plus the expansion of every
+    context token through U_k and U_v), else in the absorbed form (scores over latent + rotated numbers, values
+    over the latent)."""
     W, V = cfg["width"], cfg["vocab"]
     order, passes = dizatar_runs(cfg)
     total = 2 * V * W + passes * 2 * T * 2 * W * W
@@ -445,7 +447,11 @@ def dizatar_prefill_flops(cfg, T):
         m, f = cfg["layers"][i]["mixer"], cfg["layers"][i]["mlp"]
         H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
         total += 2 * T * (H * (dn + dr) * W + (R + dr) * W + H * dn * R + H * dv * R + W * H * dv)
-        total += H * 2 * (2 * R + dr) * (T * (T + 1) // 2)
+        d = dn + dr
+        if d % 16 == 0 and d <= 256 and dv <= d and d + dv < 2 * R + dr:
+            total += H * 2 * (d + dv) * (T * (T + 1) // 2) + 2 * T * R * H * (dn + dv)
+        else:
+            total += H * 2 * (2 * R + dr) * (T * (T + 1) // 2)
         if f:
             E, ident, top, F = f["router"]["experts"], f["router"]["identity"], f["router"]["top"], f["expert"]["ff"]
             total += 2 * T * (top * E / (E + ident) * 3 * F * W + (E + ident) * W)
