@@ -390,7 +390,7 @@ def dizatar_sizes(name):
                                 rot=dict(base=10000.0, dims=rot)),
                      mlp=dict(kind="moe", router=dict(experts=experts, identity=identity, top=top), expert=dict(ff=ff),
                               shared=dict(ff=shared)))
-        return dict(architecture="Dizatar", width=width, vocab=vocab, norm=dict(eps=1e-6), residual_mult=0.7,
+        return dict(architecture="Dizatar", width=width, vocab=vocab, norm=dict(eps=1e-6), residual_mult=0.6,
                     logit_softcap=30.0, loop=dict(start=1, stop=3, times=2), layers=[layer] * 4)
 
     def llama(width, heads, kv, ff, vocab, runs):

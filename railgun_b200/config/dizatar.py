@@ -139,7 +139,7 @@ class DizatarConfig:
         if lr is not None:
             loop = LoopConfig(lr.integer("start", minimum=0), lr.integer("stop", minimum=0),
                               lr.integer("times", minimum=1))
-            if not loop.start < loop.stop <= len(layers):
+            if not loop.start <= loop.stop <= len(layers):          # an empty span (start == stop) loops nothing
                 raise ConfigError(f"{where}: loop {loop.start}..{loop.stop} does not name layers of the {len(layers)}")
         cap = r.number("logit_softcap", None)
         return DizatarConfig(

@@ -103,6 +103,13 @@ def test_run_order_of_the_plain_model_and_of_the_package():
     assert [i for i, _ in P.layer_order(C.CASE_P)] == [0, 1, 0, 1, 0, 1, 2]
     assert [s for _, s in P.layer_order(C.CASE_P)] == [True, False, True, False, True, False, False]
     assert [i for i, _ in P.layer_order(C.CASE_N)] == [0, 1]
+    # an empty span: every layer once, nothing fed in again, the matrix still belongs to the model
+    empty = {**C.CASE_P, "loop": dict(start=1, stop=1, times=3)}
+    spec = dizatar_model_spec(DizatarConfig.from_dict(empty))
+    assert [(e.layer, e.before) for e in spec.run_order()] == [(0, -1), (1, -1), (2, -1)]
+    assert [i for i, s in P.layer_order(empty)] == [0, 1, 2] and not any(s for _, s in P.layer_order(empty))
+    from railgun_b200.parts.model import expected_tensors
+    assert "loop.in" in expected_tensors(spec)
 
 
 def test_configuration_round_trip_and_errors():
