@@ -56,15 +56,25 @@ CASE_N = dict(
             layer(mixer(16, 16, 32, 16, 128, base=500000.0), None)])
 
 # M: six heads of 48 + 32 over a latent of 80 with values of 40 (every size a different multiple of 8), one
-#    layer looped twice and one behind it.
+#    layer looped twice and one behind it; all eight router outputs chosen (no ties: bfloat16 is held to the
+#    tight bound everywhere, here for prompts in the expanded form).
 CASE_M = dict(
     architecture="Dizatar", width=72, vocab=150, norm=dict(eps=1e-5), residual_mult=0.9, logit_softcap=20.0,
     loop=dict(start=0, stop=1, times=2),
-    layers=[layer(mixer(6, 48, 32, 40, 80, base=3000.0), moe(6, 2, 2, 40, 24)),
+    layers=[layer(mixer(6, 48, 32, 40, 80, base=3000.0), moe(6, 2, 8, 40, 24)),
             layer(mixer(6, 48, 32, 40, 80, base=3000.0), None)])
 
+# A: heads of 40 + 16 (no multiple of 16, so prompts stay in the compressed form) over a latent of 64 + 16 that
+#    the tensor-core kernel takes; every router output is chosen in both layers, so no choice is ever near a tie
+#    and bfloat16 is held to the tight bound at every position.
+CASE_A = dict(
+    architecture="Dizatar", width=56, vocab=90, norm=dict(eps=1e-6), residual_mult=1.1, logit_softcap=12.0,
+    loop=dict(start=1, stop=2, times=3),
+    layers=[layer(mixer(4, 40, 16, 24, 64, base=700.0), moe(3, 2, 5, 24, 40)),
+            layer(mixer(4, 40, 16, 24, 64, base=700.0), moe(2, 1, 3, 32, None))])
+
 CASES = {"P": (CASE_P, 3, 8), "Q": (CASE_Q, 5, 16), "S": (CASE_S, 7, 4), "N": (CASE_N, 9, 32),
-         "M": (CASE_M, 11, 16)}                                                                # config, seed, page
+         "M": (CASE_M, 11, 16), "A": (CASE_A, 13, 8)}                                          # config, seed, page
 
 _made: dict = {}
 _plain: dict = {}

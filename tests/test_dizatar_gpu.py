@@ -213,7 +213,7 @@ def test_soft_cap():
 # ---- the model through the step function ----------------------------------------------------------------
 
 LENGTHS = {"P": [5, 17, 33, 70, 100, 131, 64, 48], "Q": [300, 392, 129, 257, 64, 395], "S": [1, 2, 9, 40, 3],
-           "N": [3, 90, 150, 64, 33], "M": [2, 66, 190, 31, 128]}
+           "N": [3, 90, 150, 64, 33], "M": [2, 66, 190, 31, 128], "A": [150, 7, 65, 99]}
 PORTIONS = {"Q": (130, 2, 64, 7, 128, 3, 65, 2, 33, 129)}
 MIXED = {"Q": (5, 1, 2, 70, 1, 1, 3, 140, 1, 2, 128, 17)}
 _oracle: dict = {}
@@ -285,7 +285,7 @@ def compare(rows, reqs, logits, dtype, what, case=None):
 
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["P", "Q", "S", "N", "M"])
+@pytest.mark.parametrize("name", ["P", "Q", "S", "N", "M", "A"])
 def test_replay_matches_plain(name, dtype, mode, tmp_path):
     """Whole prompts; the last 32 tokens one by one; portions down to two tokens, cut inside pages; up to four
     live requests in a pool so small that pages and slots are used again."""
