@@ -6,13 +6,20 @@ down-projection of its input, RMS-normed) and one rotated key part of
 head's score is scale * (q_plain . U_k[h] c + q_rot . k_rot), so with the
 plain query part taken through U_k[h]^T once, every head reads the same
 cache rows: scores over [c | k_rot], values = c, and the head's output is
-U_v[h] applied to the weighted sum of c.  Nothing is ever expanded per head.
+U_v[h] applied to the weighted sum of c.  In this form nothing is expanded per head.
 
   proj          one product for the queries and the down-projection
   qa[:, h, :R]  = U_k[h]^T q_plain[h]          batched product (library)
   qa[:, h, R:]  = rotate(q_rot[h]);  cache row = [rmsnorm(c) | rotate(k_rot)]   (one kernel)
   o_lat         attention over the cache                                        (kernels)
   out           = W_o concat_h(U_v[h] o_lat[h])    batched product, product
+
+That is the form single tokens always take.  Requests that bring several
+tokens attend per head to expanded keys [U_k c | k_rot] and values U_v c
+where that is cheaper and the sizes fit the flash kernel of ordinary paged
+attention: the step expands those requests' contexts from the cache into
+temporary key/value pages (``ops.latent_expand_context``) and rotates the
+queries in place; the cache itself only ever holds the compressed rows.
 """
 from __future__ import annotations
 
