@@ -318,7 +318,14 @@ def group_needs(needs: dict) -> tuple[list, dict, dict]:
     groups: list = []
     group_of: dict = {}
     states: dict = {}
+    flat = {}
     for cid, need in needs.items():
+        if isinstance(need, (tuple, list)):                 # a mixer that keeps several things: ids (cid, 0), (cid, 1), ...
+            for k, sub in enumerate(need):
+                flat[(cid, k)] = sub
+        else:
+            flat[cid] = need
+    for cid, need in flat.items():
         if need is None:
             continue
         if isinstance(need, StateNeed):
@@ -348,6 +355,7 @@ class CacheManager:
     def __init__(self, needs: dict, page_size: int, max_tokens: int, max_requests: int, dtype, device):
         import torch
         groups, self.group_of, self.state_needs = group_needs(needs)
+        self.composite = {cid: len(need) for cid, need in needs.items() if isinstance(need, (tuple, list))}
         self.groups = []
         for need, cids in groups:
             ps = int(need.page_size or page_size)

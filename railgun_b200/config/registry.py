@@ -74,3 +74,5 @@ def _ensure_builtin():
         from ..models import llama  # noqa: F401  (registers itself)
     if "Dizatar" not in _ARCHITECTURES:
         from ..models import dizatar  # noqa: F401
+    if "Rupulix" not in _ARCHITECTURES:
+        from ..models import rupulix  # noqa: F401

@@ -118,3 +118,59 @@ extern "C" int rg_softcap(float* z, float cap, long long n, void* stream) {
     return rg_launch(softcap_kernel, dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0,
                      (cudaStream_t)stream, 1, z, cap, (size_t)n);
 }
+
+// Elementwise activations of a dense feed-forward, computed in 32-bit: 0 relu(z)^2, 1 relu, 2 gelu (tanh form), 3 silu.
+__device__ __forceinline__ float act_apply(float z, int kind) {
+    switch (kind) {
+        case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+        case 1: return fmaxf(z, 0.f);
+        case 2: return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+        default: return z / (1.f + expf(-z));
+    }
+}
+
+template <typename A>
+__global__ void activation_kernel(const A* __restrict__ in, A* __restrict__ out, int kind, size_t n) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_f32<A>(act_apply(to_f32(in[i]), kind));
+}
+
+// Eight bfloat16 numbers per thread with 16-byte loads and stores.
+__global__ void activation_vec8_kernel(const bf16* __restrict__ in, bf16* __restrict__ out, int kind, size_t groups) {
+    pdl_wait();
+    pdl_trigger();
+    const size_t g = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    const uint4 v = *reinterpret_cast<const uint4*>(in + g * 8);
+    const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(v2[i]);
+        o2[i] = __floats2bfloat162_rn(act_apply(f.x, kind), act_apply(f.y, kind));
+    }
+    *reinterpret_cast<uint4*>(out + g * 8) = o;
+}
+
+extern "C" int rg_activation(const void* in, void* out, int dtype, int kind, long long n, void* stream) {
+    if (n <= 0) return 0;
+    if (kind < 0 || kind > 3) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    if (dtype == RG_DTYPE_BF16 && n % 8 == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+        const size_t groups = (size_t)n / 8;
+        return rg_launch(activation_vec8_kernel, dim3((unsigned)((groups + threads - 1) / threads)), dim3(threads), 0, s, 1,
+                         (const bf16*)in, (bf16*)out, kind, groups);
+    }
+    const unsigned blocks = (unsigned)(((size_t)n + threads - 1) / threads);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(activation_kernel<bf16>, dim3(blocks), dim3(threads), 0, s, 1, (const bf16*)in, (bf16*)out, kind,
+                         (size_t)n);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(activation_kernel<float>, dim3(blocks), dim3(threads), 0, s, 1, (const float*)in, (float*)out, kind,
+                         (size_t)n);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -13,27 +13,37 @@
 //
 // Kernels here:
 //   latent_rope_cache    per token: RMS norm of the latent part and rotation of the shared key part into the
-//                        cache row; rotation of every head's rotated query part into qa[:, :, R:]
+//                        cache row; rotation of every head's rotated query part into qa[:, :, R:]; pairs
+//                        (i, i + dims/2) or (2i, 2i + 1)
 //   latent_attention_general  one block per (token, head), all arithmetic in 32-bit, any sizes: the true
-//                        32-bit path and every shape the tensor-core kernels refuse
+//                        32-bit path and every shape the tensor-core kernels refuse; optionally a sink per
+//                        head in the softmax's denominator
 #include "common.cuh"
 
 #define LAT_THREADS 128
 #define LAT_MAX_ACC 8            // output numbers per thread of the general kernel: R <= 8 * 128
 
-// Rotation of pairs (i, i + dims/2), i < dims/2, by the angle pos * freq[i]; cs holds cos | sin of the dims/2
-// angles (32-bit, computed once per token); numbers from `dims` on pass unchanged.  src and dst hold n numbers.
+// One number of a rotated vector.  Pair p < dims/2 is (p, p + dims/2), or (2p, 2p + 1) when `interleaved`; it
+// turns by the angle pos * freq[p]: (u, v) -> (u cos - v sin, v cos + u sin).  cs holds cos | sin of the dims/2
+// angles (computed once per token); numbers from `dims` on pass unchanged.
+template <typename A>
+__device__ __forceinline__ float rotated_number(const A* __restrict__ src, int j, int dims, bool interleaved,
+                                                const float* __restrict__ cs) {
+    const int half = dims >> 1;
+    if (j >= dims) return to_f32(src[j]);
+    if (interleaved) {
+        const int p = j >> 1;
+        return (j & 1) ? to_f32(src[j]) * cs[p] + to_f32(src[j - 1]) * cs[half + p]
+                       : to_f32(src[j]) * cs[p] - to_f32(src[j + 1]) * cs[half + p];
+    }
+    if (j < half) return to_f32(src[j]) * cs[j] - to_f32(src[j + half]) * cs[half + j];
+    return to_f32(src[j]) * cs[j - half] + to_f32(src[j - half]) * cs[j];
+}
+
 template <typename A, typename B>
 __device__ __forceinline__ void rotate_pairs(const A* __restrict__ src, B* __restrict__ dst, int n, int dims,
-                                             const float* __restrict__ cs) {
-    const int half = dims >> 1;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v;
-        if (i < half) v = to_f32(src[i]) * cs[i] - to_f32(src[i + half]) * cs[half + i];
-        else if (i < dims) v = to_f32(src[i]) * cs[i - half] + to_f32(src[i - half]) * cs[i];
-        else v = to_f32(src[i]);
-        dst[i] = from_f32<B>(v);
-    }
+                                             bool interleaved, const float* __restrict__ cs) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = from_f32<B>(rotated_number(src, i, dims, interleaved, cs));
 }
 
 // proj: [T, ld] = per head [dn plain | dr rotated] query numbers, then at offset kv_off the down-projection
@@ -41,7 +51,7 @@ __device__ __forceinline__ void rotate_pairs(const A* __restrict__ src, B* __res
 template <typename A>
 __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int kv_off, A* __restrict__ qa,
                                          A* __restrict__ cache, const float* __restrict__ norm_w, float eps,
-                                         const float* __restrict__ freq, int rot_dims,
+                                         const double* __restrict__ freq, int rot_dims, int interleaved,
                                          const int* __restrict__ positions, const int* __restrict__ slots,
                                          int H, int dn, int dr, int R, A* __restrict__ q_back) {
     __shared__ float scratch[33];
@@ -50,23 +60,20 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
-    const float pos = (float)positions[t];
+    const double pos = (double)positions[t];
     const A* row = proj + (size_t)t * ld;
     const int D = R + dr;
-    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {
-        const float a = pos * freq[i];
-        cs[i] = cosf(a);
-        cs[(rot_dims >> 1) + i] = sinf(a);
+    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {      // angles in 64-bit: a handful per token
+        double sn, c;
+        sincos(pos * freq[i], &sn, &c);
+        cs[i] = (float)c;
+        cs[(rot_dims >> 1) + i] = (float)sn;
     }
     __syncthreads();
     for (int i = threadIdx.x; i < H * dr; i += blockDim.x) {     // all heads' rotated parts at once
         const int h = i / dr, j = i - h * dr;
         const A* src = row + (size_t)h * (dn + dr) + dn;
-        const int half = rot_dims >> 1;
-        float v;
-        if (j < half) v = to_f32(src[j]) * cs[j] - to_f32(src[j + half]) * cs[half + j];
-        else if (j < rot_dims) v = to_f32(src[j]) * cs[j - half] + to_f32(src[j - half]) * cs[j];
-        else v = to_f32(src[j]);
+        const float v = rotated_number(src, j, rot_dims, interleaved != 0, cs);
         if (qa) qa[((size_t)t * H + h) * D + R + j] = from_f32<A>(v);
         if (q_back) rot_q[i] = v;
     }
@@ -86,13 +93,13 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
     const float inv = rsqrtf(ss / (float)R + eps);
     A* dst = cache + (size_t)slot * D;
     for (int i = threadIdx.x; i < R; i += blockDim.x) dst[i] = from_f32<A>(to_f32(lat[i]) * inv * norm_w[i]);
-    rotate_pairs(lat + R, dst + R, dr, rot_dims, cs);
+    rotate_pairs(lat + R, dst + R, dr, rot_dims, interleaved != 0, cs);
 }
 
 // q_in_place: the rotated query parts also replace the unrotated ones in proj (qa may then be null).
 extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* qa, void* cache, int dtype,
-                                    const float* norm_w, float eps, const float* freq, int rot_dims,
-                                    const int* positions, const int* slots, int T, int H, int dn, int dr, int R,
+                                    const float* norm_w, float eps, const double* freq, int rot_dims,
+                                    int interleaved, const int* positions, const int* slots, int T, int H, int dn, int dr, int R,
                                     int q_in_place, void* stream) {
     if (T <= 0) return 0;
     if (rot_dims < 0 || rot_dims > dr || (rot_dims & 1) || R < 1 || H < 1 || rot_dims > 8192) return RG_ERR_UNSUPPORTED;
@@ -101,11 +108,11 @@ extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* 
     if (cs_bytes > 48 * 1024) return RG_ERR_UNSUPPORTED;
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const bf16*)proj, ld,
-                         kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R,
+                         kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, interleaved, positions, slots, H, dn, dr, R,
                          q_in_place ? (bf16*)proj : (bf16*)nullptr);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const float*)proj, ld,
-                         kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, positions, slots, H, dn, dr, R,
+                         kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, interleaved, positions, slots, H, dn, dr, R,
                          q_in_place ? (float*)proj : (float*)nullptr);
     return RG_ERR_UNSUPPORTED;
 }
@@ -116,7 +123,8 @@ template <typename A>
 __global__ void latent_attention_general_kernel(
         const A* __restrict__ qa, A* __restrict__ out, const A* __restrict__ cache,
         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ req_of_token,
-        const int* __restrict__ positions, int H, int R, int D, int page_size, int window, float scale) {
+        const int* __restrict__ positions, int H, int R, int D, int page_size, int window, float scale,
+        const float* __restrict__ sink) {
     extern __shared__ float smem[];
     float* qs = smem;                    // [D]
     float* ps = qs + D;                  // [LAT_THREADS]
@@ -167,6 +175,13 @@ __global__ void latent_attention_general_kernel(
         }
         __syncthreads();
     }
+    if (sink) {                          // a term of the denominator without key or value: exp(sink[h]), unscaled, once
+        const float m_new = fmaxf(m, sink[h]);
+        const float alpha = expf(m - m_new);
+        l = l * alpha + expf(sink[h] - m_new);
+#pragma unroll
+        for (int k = 0; k < LAT_MAX_ACC; ++k) acc[k] *= alpha;
+    }
     A* orow = out + ((size_t)t * H + h) * R;
     const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
@@ -179,7 +194,7 @@ __global__ void latent_attention_general_kernel(
 extern "C" int rg_latent_attention_general(
         const void* qa, void* out, const void* cache, int dtype, const int* block_table, int max_blocks,
         const int* req_of_token, const int* positions, int T, int H, int R, int D, int page_size, int window,
-        float scale, void* stream) {
+        float scale, const float* sink, void* stream) {
     if (T <= 0) return 0;
     if (R < 1 || R > LAT_MAX_ACC * LAT_THREADS || D < R || H < 1 || page_size < 1) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
@@ -188,11 +203,11 @@ extern "C" int rg_latent_attention_general(
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(latent_attention_general_kernel<bf16>, grid, dim3(LAT_THREADS), smem, s, 1,
                          (const bf16*)qa, (bf16*)out, (const bf16*)cache, block_table, max_blocks, req_of_token,
-                         positions, H, R, D, page_size, window, scale);
+                         positions, H, R, D, page_size, window, scale, sink);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(latent_attention_general_kernel<float>, grid, dim3(LAT_THREADS), smem, s, 1,
                          (const float*)qa, (float*)out, (const float*)cache, block_table, max_blocks, req_of_token,
-                         positions, H, R, D, page_size, window, scale);
+                         positions, H, R, D, page_size, window, scale, sink);
     return RG_ERR_UNSUPPORTED;
 }
 

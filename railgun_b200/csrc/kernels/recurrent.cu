@@ -1,0 +1,144 @@
+// A gated linear recurrence behind a short causal convolution (the recurrent block of Griffin: De et al.,
+// "Griffin: Mixing Gated Linear Recurrences with Local Attention for Efficient Language Models").
+//
+// Per token, from one product proj = [W_y h | W_x h] (C numbers each):
+//   g     = gelu_tanh(proj_y + b_y)                                 the gate branch
+//   xin   = proj_x + b_x
+//   u_t   = b_c + sum_k taps[:, K-1-k] xin_(t-k)                    causal, per channel, zeros before the start
+//   r, i  = sigmoid(R_b u_b + b_r), sigmoid(I_b u_b + b_i)          per block b of C / blocks channels (a batched
+//                                                                   product outside these kernels gives R_b u_b | I_b u_b)
+//   a     = exp(-c r softplus(lam))
+//   S_t   = a S_(t-1) + sqrt(1 - a^2) i u_t                         S = 0 before the first token
+//   out_t = S_t g
+// Everything after the product is 32-bit.  Between steps a request keeps, in its state slot, the last K - 1
+// values of xin (rows 0..K-2 of the slot, oldest first) and S (row K-1): state [slots, K, C] float.
+//
+// The step's tokens are packed request by request (cu_seqlens); a request whose start position is 0 begins
+// from zeros whatever its slot holds; a row whose request has slot -1 (padding of a static batch) reads zeros
+// and writes no state.
+#include "common.cuh"
+
+#define REC_THREADS 128
+#define REC_MAX_TAPS 16
+
+__device__ __forceinline__ float rec_sigmoid(float z) { return 1.f / (1.f + expf(-z)); }
+__device__ __forceinline__ float rec_softplus(float z) { return log1pf(expf(-fabsf(z))) + fmaxf(z, 0.f); }
+__device__ __forceinline__ float rec_gelu_tanh(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// u [T, C] float
+template <typename A>
+__global__ void recurrent_conv_kernel(const A* __restrict__ proj, int ld, int x_off, const float* __restrict__ xb,
+                                      const float* __restrict__ taps, const float* __restrict__ cb,
+                                      const float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                                      const int* __restrict__ req_of_token, const int* __restrict__ start_pos,
+                                      const int* __restrict__ slots, float* __restrict__ u, int C, int K) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int r = req_of_token[t];
+    const int i = t - cu_seqlens[r];
+    const int slot = slots[r];
+    const bool has_past = slot >= 0 && start_pos[r] > 0;
+    const float b = xb[c];
+    float acc = cb[c];
+    for (int k = 0; k < K; ++k) {
+        const int idx = i - k;
+        float xin;
+        if (idx >= 0) xin = to_f32(proj[(size_t)(t - k) * ld + x_off + c]) + b;
+        else xin = has_past ? state[((size_t)slot * K + (K - 1 + idx)) * C + c] : 0.f;
+        acc += taps[(size_t)c * K + (K - 1 - k)] * xin;
+    }
+    u[(size_t)t * C + c] = acc;
+}
+
+// gates [blocks, T, 2 bs] float: R_b u_b | I_b u_b.  out [T, C] rows out_ld apart, times out_scale.
+template <typename A>
+__global__ void recurrent_scan_kernel(const A* __restrict__ proj, int ld, int y_off, int x_off,
+                                      const float* __restrict__ yb, const float* __restrict__ xb,
+                                      const float* __restrict__ u, const float* __restrict__ gates,
+                                      const float* __restrict__ rb, const float* __restrict__ ib,
+                                      const float* __restrict__ lam, float decay, float* __restrict__ state,
+                                      const int* __restrict__ cu_seqlens, const int* __restrict__ start_pos,
+                                      const int* __restrict__ slots, A* __restrict__ out, int out_ld, float out_scale,
+                                      int T, int C, int K, int bs) {
+    const int r = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float sp = decay * rec_softplus(lam[c]);
+    const float byc = yb[c], bxc = xb[c], brc = rb[c], bic = ib[c];
+    const int blk = c / bs, o = c - blk * bs;
+    pdl_wait();
+    pdl_trigger();
+    const int lo = cu_seqlens[r], hi = cu_seqlens[r + 1];
+    const int slot = slots[r];
+    const bool has_past = slot >= 0 && start_pos[r] > 0;
+    float* st = slot >= 0 ? state + (size_t)slot * K * C : nullptr;
+    float S = has_past ? st[(size_t)(K - 1) * C + c] : 0.f;
+    const float* grow = gates + ((size_t)blk * T) * 2 * bs + o;
+    for (int t = lo; t < hi; ++t) {
+        const float gr = grow[(size_t)t * 2 * bs] + brc;
+        const float gi = grow[(size_t)t * 2 * bs + bs] + bic;
+        const float log_a = -sp * rec_sigmoid(gr);
+        const float a = expf(log_a);
+        const float m = sqrtf(-expm1f(2.f * log_a));                  // sqrt(1 - a^2) without cancellation near a = 1
+        S = a * S + m * rec_sigmoid(gi) * u[(size_t)t * C + c];
+        const float g = rec_gelu_tanh(to_f32(proj[(size_t)t * ld + y_off + c]) + byc);
+        out[(size_t)t * out_ld + c] = from_f32<A>(S * g * out_scale);
+    }
+    if (!st) return;
+    st[(size_t)(K - 1) * C + c] = S;
+    // the last K - 1 inputs of the convolution: from this step's tokens, and before them from the old tail
+    const int n = hi - lo;
+    float tail[REC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < REC_MAX_TAPS; ++j) {
+        if (j < K - 1) {
+            const int src = n - (K - 1) + j;
+            if (src >= 0) tail[j] = to_f32(proj[(size_t)(lo + src) * ld + x_off + c]) + bxc;
+            else tail[j] = has_past ? st[(size_t)(n + j) * C + c] : 0.f;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < REC_MAX_TAPS; ++j)
+        if (j < K - 1) st[(size_t)j * C + c] = tail[j];
+}
+
+extern "C" int rg_recurrent_conv(const void* proj, int dtype, int ld, int x_off, const float* xb, const float* taps,
+                                 const float* cb, const float* state, const int* cu_seqlens, const int* req_of_token,
+                                 const int* start_pos, const int* slots, float* u, int T, int C, int K, void* stream) {
+    if (T <= 0) return 0;
+    if (C < 1 || K < 1 || K > REC_MAX_TAPS) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(T, (C + REC_THREADS - 1) / REC_THREADS);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(recurrent_conv_kernel<bf16>, grid, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, x_off, xb,
+                         taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(recurrent_conv_kernel<float>, grid, dim3(REC_THREADS), 0, s, 1, (const float*)proj, ld, x_off, xb,
+                         taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K);
+    return RG_ERR_UNSUPPORTED;
+}
+
+extern "C" int rg_recurrent_scan(const void* proj, int dtype, int ld, int y_off, int x_off, const float* yb,
+                                 const float* xb, const float* u, const float* gates, const float* rb, const float* ib,
+                                 const float* lam, float decay, float* state, const int* cu_seqlens,
+                                 const int* start_pos, const int* slots, void* out, int out_ld, float out_scale, int T,
+                                 int R, int C, int K, int bs, void* stream) {
+    if (T <= 0 || R <= 0) return 0;
+    if (C < 1 || K < 1 || K > REC_MAX_TAPS || bs < 1 || C % bs) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(R, (C + REC_THREADS - 1) / REC_THREADS);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(recurrent_scan_kernel<bf16>, grid, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, y_off,
+                         x_off, yb, xb, u, gates, rb, ib, lam, decay, state, cu_seqlens, start_pos, slots, (bf16*)out,
+                         out_ld, out_scale, T, C, K, bs);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(recurrent_scan_kernel<float>, grid, dim3(REC_THREADS), 0, s, 1, (const float*)proj, ld, y_off,
+                         x_off, yb, xb, u, gates, rb, ib, lam, decay, state, cu_seqlens, start_pos, slots, (float*)out,
+                         out_ld, out_scale, T, C, K, bs);
+    return RG_ERR_UNSUPPORTED;
+}

@@ -88,6 +88,10 @@ class _CacheViews:
             self._views[cid] = CacheView(cid, group=cache.group_of[cid], kv=t, page_size=cache.page_size_of(cid))
         for cid, t in cache.state.items():
             self._views[cid] = CacheView(cid, state=t)
+        # a mixer that asked for a tuple of needs sees one view per need
+        for cid, n in cache.composite.items():
+            self._views[cid] = CacheView(cid, parts=tuple(self._views.get((cid, k)) or CacheView(cid)
+                                                          for k in range(n)))
         self._none = {}
 
     def view(self, cid):

@@ -17,27 +17,14 @@ from __future__ import annotations
 
 from ..config.dizatar import DizatarConfig
 from ..config.registry import Architecture, register_architecture
-from ..parts.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry, SubLayer
+from ..parts.spec import LayerSpec, ModelSpec, PartSpec, SubLayer, looped_run_order
 
 
 def dizatar_run_order(n_layers: int, loop) -> tuple:
     """Schedule entries: the layers before the span, the span ``times`` times
     (every pass with caches of its own, its first layer behind stream
     operation 0), the layers after it."""
-    if loop is None:
-        return tuple(ScheduleEntry(i, i) for i in range(n_layers))
-    order, cache = [], 0
-    for i in range(loop.start):
-        order.append(ScheduleEntry(i, cache))
-        cache += 1
-    for _ in range(loop.times):
-        for i in range(loop.start, loop.stop):
-            order.append(ScheduleEntry(i, cache, True, 0 if i == loop.start else -1))
-            cache += 1
-    for i in range(loop.stop, n_layers):
-        order.append(ScheduleEntry(i, cache))
-        cache += 1
-    return tuple(order)
+    return looped_run_order(n_layers, loop, before=0)
 
 
 def dizatar_model_spec(c: DizatarConfig) -> ModelSpec:

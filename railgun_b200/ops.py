@@ -210,14 +210,15 @@ def softcap_(logits: torch.Tensor, cap: float) -> torch.Tensor:
 
 def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa, cache, norm_w: torch.Tensor, eps: float,
                       freq: torch.Tensor, rot_dims: int, positions: torch.Tensor, slots, H: int, dn: int, dr: int,
-                      R: int, q_in_place: bool = False) -> None:
+                      R: int, q_in_place: bool = False, interleaved: bool = False) -> None:
     """Per token of ``proj`` [T, H (dn + dr) + R + dr] (queries per head as
     [dn plain | dr rotated], then at ``kv_off`` the compressed key/value vector
     [R | dr]): rotate every head's rotated part into ``qa`` [T, H, R + dr][:, :, R:],
     and write [RMS norm of the R latent numbers times ``norm_w`` | rotated key
     part] into row ``slots[t]`` of ``cache`` [pages, page, R + dr] (``slots``
-    None or a negative slot: no write).  Rotation: pairs (i, i + rot_dims / 2) by
-    position * ``freq[i]``, in 32-bit.  ``q_in_place``: the rotated parts also
+    None or a negative slot: no write).  Rotation: pairs (i, i + rot_dims / 2), or
+    (2i, 2i + 1) with ``interleaved``, by position * ``freq[i]`` (64-bit
+    frequencies and angles, 32-bit rotation).  ``q_in_place``: the rotated parts also
     replace the unrotated ones in ``proj`` (``qa`` may then be None)."""
     _check(proj, "proj")
     if qa is None and not q_in_place:
@@ -225,7 +226,7 @@ def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa, cache, norm_w: torch.
     if qa is not None:
         _check(qa, "qa", proj.dtype)
     _check(norm_w, "norm_w", torch.float32)
-    _check(freq, "freq", torch.float32)
+    _check(freq, "freq", torch.float64)
     _check(positions, "positions", torch.int32)
     T = proj.shape[0]
     D = R + dr
@@ -242,7 +243,8 @@ def latent_rope_cache(proj: torch.Tensor, kv_off: int, qa, cache, norm_w: torch.
             raise KernelError(f"latent cache rows hold {cache.shape[-1]} numbers, the mixer writes {D}")
     _ok(_fn("attention_latent", "rg_latent_rope_cache")(
         _ptr(proj), c_int(proj.stride(0)), c_int(kv_off), _ptr(qa), _ptr(cache if slots is not None else None),
-        c_int(_dtype_code(proj)), _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions),
+        c_int(_dtype_code(proj)), _ptr(norm_w), c_float(eps), _ptr(freq), c_int(rot_dims),
+        c_int(1 if interleaved else 0), _ptr(positions),
         _ptr(slots), c_int(T), c_int(H), c_int(dn), c_int(dr), c_int(R), c_int(1 if q_in_place else 0), _stream()),
         "latent_rope_cache")
 
@@ -282,9 +284,10 @@ def latent_expand_context(cache: torch.Tensor, block_table: torch.Tensor, cu_seq
 
 def latent_attention_general(qa: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
                              req_of_token: torch.Tensor, positions: torch.Tensor, R: int, window: int,
-                             scale: float) -> torch.Tensor:
+                             scale: float, sink: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of ``qa`` [T, H, D] over the latent cache [pages, page, D]: the
     scores use all D numbers of a cache row, the values are its first R.
+    ``sink`` [H] float32: exp(sink[h]) joins head h's softmax denominator.
     Returns [T, H, R].  32-bit arithmetic, any sizes with R <= 1024."""
     _check(qa, "qa")
     _check(cache, "cache", qa.dtype)
@@ -294,11 +297,15 @@ def latent_attention_general(qa: torch.Tensor, cache: torch.Tensor, block_table:
     T, H, D = qa.shape
     if cache.dim() != 3 or cache.shape[2] != D or R > D:
         raise KernelError(f"latent cache {tuple(cache.shape)} does not match queries of {D} numbers, latent {R}")
+    if sink is not None:
+        _check(sink, "sink", torch.float32)
+        if sink.numel() != H:
+            raise KernelError(f"{sink.numel()} sinks for {H} heads")
     out = torch.empty((T, H, R), dtype=qa.dtype, device=qa.device)
     _ok(_fn("attention_latent", "rg_latent_attention_general")(
         _ptr(qa), _ptr(out), _ptr(cache), c_int(_dtype_code(qa)), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(req_of_token), _ptr(positions), c_int(T), c_int(H), c_int(R), c_int(D), c_int(cache.shape[1]),
-        c_int(window or 0), c_float(scale), _stream()), "latent_attention_general")
+        c_int(window or 0), c_float(scale), _ptr(sink), _stream()), "latent_attention_general")
     return out
 
 
@@ -471,6 +478,170 @@ def moe_combine(x: torch.Tensor, y, shared, ids: torch.Tensor, weights: torch.Te
     _ok(_fn("moe", "rg_moe_combine")(_ptr(x), _ptr(y), _ptr(shared), c_int(_dtype_code(x)), _ptr(ids), _ptr(weights),
                                      _ptr(pair_pos), _ptr(out), c_int(T), c_int(W), c_int(num_experts), c_int(top),
                                      _stream()), "moe_combine")
+    return out
+
+
+
+# ---- hyper-connections, talking-heads attention, the gated recurrence, plain activations ---------------
+
+def hyper_step(copies, x0, y, mix, outc, inc, norm_w, eps: float, out_dtype, out: torch.Tensor | None = None):
+    """One pass over the copies of a hyper-connected residual stream ``copies`` [T, S, W] (32-bit, in
+    place).  With ``x0`` [T, W]: every copy becomes x0 (the start).  With ``y`` [T, W]: every copy t becomes
+    sum_s ``mix``[s, t] copy_s + ``outc``[t] y, all from the old copies.  Then u = sum_s ``inc``[s] copy_s
+    (``inc`` None: the plain sum) is returned RMS-normed with ``norm_w`` in ``out_dtype``, or unnormed when
+    ``norm_w`` is None; nothing is returned when ``out_dtype`` is None."""
+    _check(copies, "copies", torch.float32)
+    T, S, W = copies.shape
+    for t, name, n in ((mix, "mix", S * S), (outc, "out", S), (inc, "in", S), (norm_w, "norm weight", W)):
+        if t is not None:
+            _check(t, name, torch.float32)
+            if t.numel() != n:
+                raise KernelError(f"hyper_step: {name} has {t.numel()} elements, expected {n}")
+    for t, name in ((x0, "x0"), (y, "y")):
+        if t is not None:
+            _check(t, name)
+            if t.shape != (T, W):
+                raise KernelError(f"hyper_step: {name} {tuple(t.shape)} does not match copies {tuple(copies.shape)}")
+    if x0 is not None and x0.dtype != torch.float32:
+        raise KernelError("hyper_step: x0 must be float32")
+    if out is None and out_dtype is not None:
+        out = torch.empty((T, W), dtype=out_dtype, device=copies.device)
+    if out is not None and (out.shape != (T, W) or out.stride(1) != 1):
+        raise KernelError("hyper_step: out must be [T, W] with unit column stride")
+    _ok(_fn("hyper", "rg_hyper_step")(
+        _ptr(copies), _ptr(x0), _ptr(y), c_int(_dtype_code(y) if y is not None else 0), _ptr(mix), _ptr(outc), _ptr(inc),
+        _ptr(norm_w), c_float(eps), _ptr(out), c_int(_dtype_code(out) if out is not None else 0),
+        c_int(out.stride(0) if out is not None else W), c_int(T), c_int(S), c_int(W), _stream()), "hyper_step")
+    return out
+
+
+def talking_prepare(qkv: torch.Tensor, q_out: torch.Tensor, cache, q_norm, k_norm, eps: float, freq: torch.Tensor,
+                    rot_dims: int, positions: torch.Tensor, slots, H: int, G: int, d: int, dv: int) -> None:
+    """Per token of ``qkv`` [T, H d + G d + G dv]: every q and k head is RMS-normed over its d numbers
+    (``q_norm`` / ``k_norm`` [d] float32, None: no norm) and its first ``rot_dims`` numbers are rotated in
+    pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64); q goes to ``q_out`` [T, H, d], the keys
+    and the values to row ``slots[t]`` of ``cache`` [pages, page, G d + G dv] (negative slot or None: no write)."""
+    _check(qkv, "qkv")
+    _check(q_out, "q_out", qkv.dtype)
+    _check(freq, "freq", torch.float64)
+    _check(positions, "positions", torch.int32)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (H + G) * d + G * dv or q_out.shape != (T, H, d) or positions.numel() != T:
+        raise KernelError(f"talking_prepare: qkv {tuple(qkv.shape)} does not match {H} + {G} heads of {d}, values of {dv}")
+    for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if w is not None:
+            _check(w, name, torch.float32)
+            if w.numel() != d:
+                raise KernelError(f"talking_prepare: {name} has {w.numel()} elements, heads have {d}")
+    if (q_norm is None) != (k_norm is None):
+        raise KernelError("talking_prepare: q and k are normed together or not at all")
+    if freq.numel() < rot_dims // 2:
+        raise KernelError("talking_prepare: frequency table too short")
+    if slots is not None:
+        _check(slots, "slots", torch.int32)
+        _check(cache, "cache", qkv.dtype)
+        if cache.shape[-1] != G * (d + dv):
+            raise KernelError(f"cache rows hold {cache.shape[-1]} numbers, the mixer writes {G * (d + dv)}")
+    _ok(_fn("attention_talking", "rg_talking_prepare")(
+        _ptr(qkv), c_int(_dtype_code(qkv)), c_int(qkv.stride(0)), _ptr(q_out), _ptr(cache if slots is not None else None),
+        _ptr(q_norm), _ptr(k_norm), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions), _ptr(slots), c_int(T),
+        c_int(H), c_int(G), c_int(d), c_int(dv), _stream()), "talking_prepare")
+
+
+def _check_out_view(out, T: int, n: int, dtype, what: str):
+    if not out.is_cuda or out.dtype != dtype or out.dim() != 2 or out.shape != (T, n) or out.stride(1) != 1:
+        raise KernelError(f"{what}: out must be a CUDA [{T}, {n}] view of {dtype} with unit column stride")
+
+
+def talking_attention_general(q: torch.Tensor, cache: torch.Tensor, talk, block_table: torch.Tensor,
+                              req_of_token: torch.Tensor, positions: torch.Tensor, G: int, dv: int, window: int,
+                              scale: float, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
+    """Attention of ``q`` [T, H, d] over cache rows [pages, page, G d + G dv] with the heads' scores mixed by
+    ``talk`` [H, H] (float32; None: no mixing) before the softmax.  Returns [T, H dv] times ``out_scale``
+    (``out``: a view to write into, rows may be further apart).  32-bit arithmetic, H dv <= 4096."""
+    _check(q, "q")
+    _check(cache, "cache", q.dtype)
+    _check(block_table, "block_table", torch.int32)
+    _check(req_of_token, "req_of_token", torch.int32)
+    _check(positions, "positions", torch.int32)
+    T, H, d = q.shape
+    if cache.dim() != 3 or cache.shape[2] != G * (d + dv) or H % G:
+        raise KernelError(f"talking attention: cache {tuple(cache.shape)} does not match {G} heads of {d} + {dv}")
+    if talk is not None:
+        _check(talk, "talk", torch.float32)
+        if talk.shape != (H, H):
+            raise KernelError(f"talking attention: mixing matrix {tuple(talk.shape)} for {H} heads")
+    if out is None:
+        out = torch.empty((T, H * dv), dtype=q.dtype, device=q.device)
+    _check_out_view(out, T, H * dv, q.dtype, "talking attention")
+    _ok(_fn("attention_talking", "rg_talking_attention_general")(
+        _ptr(q), _ptr(out), c_int(out.stride(0)), c_float(out_scale), _ptr(cache), c_int(_dtype_code(q)), _ptr(talk),
+        _ptr(block_table), c_int(block_table.shape[1]), _ptr(req_of_token), _ptr(positions), c_int(T), c_int(H), c_int(G),
+        c_int(d), c_int(dv), c_int(cache.shape[1]), c_int(window or 0), c_float(scale), _stream()),
+        "talking_attention_general")
+    return out
+
+
+def recurrent_conv(proj: torch.Tensor, x_off: int, xb: torch.Tensor, taps: torch.Tensor, cb: torch.Tensor,
+                   state: torch.Tensor, batch) -> torch.Tensor:
+    """u [T, C] float32: the causal convolution (``taps`` [C, K], bias ``cb``) of proj[:, x_off:x_off + C] + ``xb``
+    per channel along each request's tokens, continued from the request's state slot (``state`` [slots, K, C]:
+    rows 0..K-2 the last inputs) unless the request starts at position 0."""
+    _check(proj, "proj")
+    for t, name in ((xb, "xb"), (taps, "taps"), (cb, "cb"), (state, "state")):
+        _check(t, name, torch.float32)
+    C, K = taps.shape
+    T = proj.shape[0]
+    if state.shape[1:] != (K, C) or proj.shape[1] < x_off + C or xb.numel() != C or cb.numel() != C:
+        raise KernelError("recurrent_conv: sizes do not match")
+    u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    _ok(_fn("recurrent", "rg_recurrent_conv")(
+        _ptr(proj), c_int(_dtype_code(proj)), c_int(proj.stride(0)), c_int(x_off), _ptr(xb), _ptr(taps), _ptr(cb),
+        _ptr(state), _ptr(batch.cu_seqlens), _ptr(batch.req_of_token), _ptr(batch.start_pos), _ptr(batch.state_slots),
+        _ptr(u), c_int(T), c_int(C), c_int(K), _stream()), "recurrent_conv")
+    return u
+
+
+def recurrent_scan(proj: torch.Tensor, y_off: int, x_off: int, yb, xb, u: torch.Tensor, gates: torch.Tensor, rb, ib, lam,
+                   decay: float, state: torch.Tensor, batch, out: torch.Tensor | None = None,
+                   out_scale: float = 1.0) -> torch.Tensor:
+    """The recurrence S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t along each request's tokens, with
+    a = exp(-``decay`` sigmoid(gates_r + rb) softplus(lam)) and i = sigmoid(gates_i + ib) (``gates``
+    [blocks, T, 2 bs] float32), from the request's state (row K-1 of its slot) or from zero at position 0;
+    returns S_t gelu_tanh(proj[:, y_off:] + yb) times ``out_scale`` as [T, C] in proj's type, and leaves S and
+    the convolution's last K-1 inputs in the slot."""
+    _check(proj, "proj")
+    for t, name in ((yb, "yb"), (xb, "xb"), (u, "u"), (gates, "gates"), (rb, "rb"), (ib, "ib"), (lam, "lam"),
+                    (state, "state")):
+        _check(t, name, torch.float32)
+    T, C = u.shape
+    K = state.shape[1]
+    blocks, bs = gates.shape[0], gates.shape[2] // 2
+    if gates.shape != (blocks, T, 2 * bs) or blocks * bs != C or state.shape[2] != C or proj.shape[0] != T:
+        raise KernelError("recurrent_scan: sizes do not match")
+    if out is None:
+        out = torch.empty((T, C), dtype=proj.dtype, device=proj.device)
+    _check_out_view(out, T, C, proj.dtype, "recurrent_scan")
+    R = batch.cu_seqlens.numel() - 1
+    _ok(_fn("recurrent", "rg_recurrent_scan")(
+        _ptr(proj), c_int(_dtype_code(proj)), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(yb), _ptr(xb),
+        _ptr(u), _ptr(gates), _ptr(rb), _ptr(ib), _ptr(lam), c_float(decay), _ptr(state), _ptr(batch.cu_seqlens),
+        _ptr(batch.start_pos), _ptr(batch.state_slots), _ptr(out), c_int(out.stride(0)), c_float(out_scale), c_int(T),
+        c_int(R), c_int(C), c_int(K), c_int(bs), _stream()), "recurrent_scan")
+    return out
+
+
+ACTIVATIONS = {"relu2": 0, "relu": 1, "gelu_tanh": 2, "silu": 3}
+
+
+def activation(x: torch.Tensor, kind: str, in_place: bool = True) -> torch.Tensor:
+    """Elementwise activation computed in 32-bit: relu2 (the square of relu), relu, gelu_tanh, silu."""
+    _check(x, "x")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"unknown activation {kind!r}; known: {sorted(ACTIVATIONS)}")
+    out = x if in_place else torch.empty_like(x)
+    _ok(_fn("activation", "rg_activation")(_ptr(x), _ptr(out), c_int(_dtype_code(x)), c_int(ACTIVATIONS[kind]),
+                                           c_longlong(x.numel()), _stream()), "activation")
     return out
 
 

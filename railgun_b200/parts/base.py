@@ -87,7 +87,8 @@ class Mixer(Part):
     """Mixes information between positions of a request.
 
     ``cache_need(params)`` (class method) says what it keeps between steps: a
-    ``PagedKVNeed``, a ``StateNeed`` or None.  ``forward(x, batch, cache,
+    ``PagedKVNeed``, a ``StateNeed``, a tuple of those (the mixer's cache view
+    then has one view per need in ``cache.parts``) or None.  ``forward(x, batch, cache,
     writes)`` takes the normed rows [T, H] of the step's tokens and returns
     [T, H]; ``cache`` is a ``CacheView`` of what the need asked for; ``writes``
     False means the layer reads a cache that another layer fills.
@@ -141,18 +142,28 @@ class CacheView:
     kv: object = None          # [pages, 2, kv_heads, page_size, head_dim]
     page_size: int = 0
     state: object = None       # [max_requests, *shape] of a StateNeed
+    parts: tuple = ()          # for a mixer that asked for a tuple of needs: one view per need, in that order
 
 
 class Stream:
     """The residual stream during a step: the 32-bit sum and the last part's
     output, not yet added (it is added inside the next norm's kernel)."""
 
-    __slots__ = ("resid", "pending", "kept")
+    __slots__ = ("resid", "pending", "kept", "copies", "closer")
 
     def __init__(self, resid):
         self.resid = resid
         self.pending = None
         self.kept = {}              # what stream operations keep from the start of the step, by operation
+        self.copies = None          # [T, S, H] 32-bit: the copies of the stream, for an arrangement that keeps several
+        self.closer = None          # set by such an arrangement: folds the copies back into ``resid``
+
+    def close(self):
+        """Leave the stream as one 32-bit sum in ``resid`` (with maybe something pending), whatever
+        form the arrangements kept it in while the layers ran."""
+        if self.closer is not None:
+            closer, self.closer = self.closer, None
+            closer(self)
 
 
 class StreamOp(Part):
@@ -172,7 +183,19 @@ class StreamOp(Part):
 
 class Arrangement:
     """How a layer's parts are wired around the residual stream.
-    ``run(layer, stream, batch, cache, writes)`` updates the stream."""
+    ``run(layer, stream, batch, cache, writes)`` updates the stream.  An
+    arrangement with tensors of its own names them per branch in
+    ``tensor_specs(sublayer, prefix)`` (a class method; ``sublayer.wiring``
+    holds what the model description says about the branch) and builds what
+    it needs from them in ``bind``, whose result ``run`` finds as the built
+    branch's ``wiring``."""
+
+    @classmethod
+    def tensor_specs(cls, sublayer, prefix: str) -> dict:
+        return {}
+
+    def bind(self, sublayer, prefix: str, env, tensors):
+        return None
 
     def run(self, layer, stream, batch, cache, writes):
         raise NotImplementedError

@@ -13,6 +13,14 @@ multiplier, a per-feature layer scale) are part of the post-norm's weight.
 The post-norm, the 32-bit addition and the next branch's norm are one kernel
 (ops.PendingNormed).
 
+"hyper": S copies of the residual stream instead of one (hyper-connections).
+A branch reads u = sum_s a[s] x_s through its norm, and its output y changes
+every copy at once: x_t <- sum_s M[s, t] x_s + b[t] y, with a [S], M [S, S]
+(indexed [from, to]) and b [S] tensors of the branch.  All copies start as the
+embedding's output and are summed into one stream at the end.  The update by
+one branch and the read of the next are one kernel (ops.hyper_step), as the
+pre-norm block's addition lives in the next norm's kernel.
+
 "reinject" (a stream operation): x <- W [x; x0] with x0 the embedding's
 output, for models that feed the input again at the start of a pass over a
 span of layers.
@@ -48,6 +56,63 @@ class Sandwich(Arrangement):
             stream.pending = ops.PendingNormed(y, b.post_norm.weight, b.post_norm.eps)
 
 
+class HyperWiring:
+    """One branch's hyper-connection coefficients, 32-bit on the device."""
+
+    def __init__(self, a, M, b):
+        self.a, self.M, self.b = a, M, b
+
+
+class Hyper(Arrangement):
+    """A branch's ``wiring``: ``streams`` (S) and ``name`` (its tensors are
+    ``<prefix><name>.in`` [S], ``.out`` [S] and ``.mix`` [S, S])."""
+
+    @classmethod
+    def tensor_specs(cls, sublayer, prefix):
+        w = sublayer.wiring
+        if not w:
+            raise ValueError("the 'hyper' arrangement needs `wiring` (streams, name) on every branch")
+        S, n = int(w["streams"]), prefix + w["name"]
+        return {n + ".in": TensorSpec((S,), init="norm"), n + ".out": TensorSpec((S,), init="norm"),
+                n + ".mix": TensorSpec((S, S), init="eye")}
+
+    def bind(self, sublayer, prefix, env, tensors):
+        n = prefix + sublayer.wiring["name"]
+        get = lambda x: tensors.get(n + x, torch.float32).contiguous()
+        return HyperWiring(get(".in"), get(".mix"), get(".out"))
+
+    @staticmethod
+    def _fold(stream):
+        """The copies' sum (with the last branch's update) becomes the one stream again."""
+        y, w = stream.pending if stream.pending is not None else (None, None)
+        stream.resid = ops.hyper_step(stream.copies, None, y, w.M if w else None, w.b if w else None, None, None, 0.0,
+                                      torch.float32)
+        stream.pending, stream.copies = None, None
+
+    def run(self, layer, stream, batch, cache, writes):
+        for b in layer.branches:
+            w = b.wiring
+            weight, eps = b.norm.weight, b.norm.eps
+            if stream.copies is None:
+                # the first branch of the step: every copy is the embedding's output
+                if stream.pending is not None:
+                    raise ValueError("the 'hyper' arrangement starts from a stream with nothing pending")
+                T, W = stream.resid.shape
+                stream.copies = torch.empty((T, w.a.numel(), W), dtype=torch.float32, device=stream.resid.device)
+                h = ops.hyper_step(stream.copies, stream.resid, None, None, None, w.a, weight, eps, self_dtype(b))
+                stream.resid = None
+                stream.closer = self._fold
+            else:
+                y, prev = stream.pending
+                h = ops.hyper_step(stream.copies, None, y, prev.M, prev.b, w.a, weight, eps, self_dtype(b))
+            y = b.part.forward(h, batch, cache, writes) if b.role == "mixer" else b.part.forward(h, batch)
+            stream.pending = (y, w)
+
+
+def self_dtype(branch):
+    return branch.part.env.dtype
+
+
 class Reinject(StreamOp):
     """params: ``hidden_size``, ``name`` (the matrix [H, 2 H], the stream's half first)."""
 
@@ -77,4 +142,5 @@ class Reinject(StreamOp):
 
 register_arrangement("prenorm", PreNorm)
 register_arrangement("sandwich", Sandwich)
+register_arrangement("hyper", Hyper)
 register_stream_op("reinject", Reinject)

@@ -33,18 +33,22 @@ from .registry import register_mixer
 
 
 def rotary_frequencies(dims: int, base: float) -> torch.Tensor:
-    """f_i = base^(-2i/dims), i < dims/2: computed in 64-bit, stored in 32-bit."""
+    """f_i = base^(-2i/dims), i < dims/2, in 64-bit (the kernels multiply by the position in 64-bit too)."""
     i = torch.arange(dims // 2, dtype=torch.float64)
-    return (float(base) ** (-2.0 * i / dims)).to(torch.float32)
+    return float(base) ** (-2.0 * i / dims)
 
 
 class LatentAttention(Mixer):
     """params: ``hidden_size``, ``num_heads``, ``head_dim`` (unrotated query/key
     numbers per head), ``rot_dim`` (rotated ones), ``v_dim``, ``kv_rank``,
-    ``scale``, ``rot_dims`` (how many of the rotated part's numbers are rotated,
-    in pairs (i, i + rot_dims/2)), ``rot_base``, ``eps`` (of the latent's norm),
-    ``window`` (0: none), ``names`` (optional: tensor names after the prefix for
-    q, dkv, dkv_norm, uk, uv, o)."""
+    ``scale``, ``rot_dims`` (how many of the rotated part's numbers are rotated),
+    ``rot_layout`` ("half": pairs (i, i + rot_dims/2), the default; "interleaved":
+    pairs (2i, 2i + 1)), ``rot_base``, ``eps`` (of the latent's norm), ``window``
+    (0: none; else a query sees itself and the window - 1 positions before it),
+    ``sink`` (optional: the name after the prefix of a tensor [heads]; exp of
+    head h's number joins the denominator of h's softmax, with no key and no
+    value), ``names`` (optional: tensor names after the prefix for q, dkv,
+    dkv_norm, uk, uv, o)."""
 
     NAMES = dict(q="mix.q", dkv="mix.dkv", dkv_norm="mix.dkv.norm", uk="mix.uk", uv="mix.uv", o="mix.o")
 
@@ -57,7 +61,9 @@ class LatentAttention(Mixer):
         W, H, dn, dr, dv, R = (p["hidden_size"], p["num_heads"], p["head_dim"], p["rot_dim"], p["v_dim"],
                                p["kv_rank"])
         n = cls._names(p, prefix)
+        sink = {prefix + p["sink"]: TensorSpec((H,))} if p.get("sink") else {}
         return {
+            **sink,
             n["q"]: TensorSpec((H * (dn + dr), W)),
             n["dkv"]: TensorSpec((R + dr, W)),
             n["dkv_norm"]: TensorSpec((R,), init="norm"),
@@ -84,6 +90,11 @@ class LatentAttention(Mixer):
         self.window = int(p.get("window") or 0)
         self.scale = float(p["scale"])
         self.eps = float(p["eps"])
+        layout = p.get("rot_layout") or "half"
+        if layout not in ("half", "interleaved"):
+            raise ValueError(f"rotation layout {layout!r} is not known: 'half' or 'interleaved'")
+        self.interleaved = layout == "interleaved"
+        self.sink = tensors.get(prefix + p["sink"], torch.float32).contiguous() if p.get("sink") else None
         n = self._names(p, prefix)
         self.w_proj = torch.cat([tensors.get(n["q"], env.dtype), tensors.get(n["dkv"], env.dtype)], dim=0).contiguous()
         tensors.drop(n["q"], n["dkv"])
@@ -98,7 +109,7 @@ class LatentAttention(Mixer):
         # per key and head instead of 2 R + dr) through the dense model's flash kernel, where the sizes fit it.
         d = self.dn + self.dr
         self.expands_prompts = (env.dtype == torch.bfloat16 and d % 16 == 0 and 16 <= d <= 256 and self.dv <= d
-                                and self.window == 0 and d + self.dv < 2 * self.R + self.dr)
+                                and self.window == 0 and self.sink is None and d + self.dv < 2 * self.R + self.dr)
         if self.expands_prompts:
             self.w_uk_flat = tensors.get(n["uk"], env.dtype)                                # [H dn, R]
             self.w_uv_flat = tensors.get(n["uv"], env.dtype)                                # [H dv, R]
@@ -117,7 +128,7 @@ class LatentAttention(Mixer):
         q_plain = proj[:, :self.kv_off].view(T, H, dn + dr)[:, :, :dn].transpose(0, 1)     # [H, T, dn], no copy
         torch.bmm(q_plain, self.w_uk, out=qa[:, :, :R].transpose(0, 1))
         ops.latent_rope_cache(proj, self.kv_off, qa, cache.kv, self.norm_w, self.eps, self.freq, self.rot_dims,
-                              batch.positions, slots, H, dn, dr, R)
+                              batch.positions, slots, H, dn, dr, R, interleaved=self.interleaved)
         o_lat = self.attend(qa, batch, cache)                                              # [T, H, R]
         heads = torch.empty((T, H * dv), dtype=proj.dtype, device=proj.device)
         torch.bmm(o_lat.transpose(0, 1), self.w_uv_t, out=heads.view(T, H, dv).transpose(0, 1))
@@ -143,7 +154,7 @@ class LatentAttention(Mixer):
             q_plain = proj[:, :self.kv_off].view(T, H, d)[:, :, :dn].transpose(0, 1)
             torch.bmm(q_plain, self.w_uk, out=qa[:, :, :R].transpose(0, 1))
         ops.latent_rope_cache(proj, self.kv_off, qa, cache.kv, self.norm_w, self.eps, self.freq, self.rot_dims,
-                              batch.positions, slots, H, dn, dr, R, q_in_place=True)
+                              batch.positions, slots, H, dn, dr, R, q_in_place=True, interleaved=self.interleaved)
         if batch.num_decode_rows:
             n = batch.num_decode_rows
             o_lat = torch.zeros((T, H, R), dtype=proj.dtype, device=proj.device)
@@ -166,9 +177,9 @@ class LatentAttention(Mixer):
         64 / heads tokens, single tokens with their contexts cut into shares); everything else, and all of the
         32-bit path, through the general kernel."""
         table = batch.block_table[cache.group]
-        if not ops.latent_attention_mma_ok(qa.dtype, self.H, self.R, self.D):
+        if self.sink is not None or not ops.latent_attention_mma_ok(qa.dtype, self.H, self.R, self.D):
             return ops.latent_attention_general(qa, cache.kv, table, batch.req_of_token, batch.positions, self.R,
-                                                self.window, self.scale)
+                                                self.window, self.scale, self.sink)
         out = torch.empty((qa.shape[0], self.H, self.R), dtype=qa.dtype, device=qa.device)
         chunks = -(-self.H // 64)
         args = (batch.req_of_token, batch.positions, self.R, self.window, self.scale)

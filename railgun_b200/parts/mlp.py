@@ -61,4 +61,30 @@ class SwiGLU(FeedForward):
         return ops.PendingLinear(act, self.w_down) if defer else ops.linear(act, self.w_down)
 
 
+class DenseMLP(FeedForward):
+    """down(act(up(x))) without a gate.  params: ``hidden_size``,
+    ``intermediate_size``, ``activation`` ("relu2": the square of relu, "relu",
+    "gelu_tanh", "silu"), ``names`` (the up and down matrices' names after the
+    prefix)."""
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        H, I = p["hidden_size"], p["intermediate_size"]
+        up, down = p["names"]
+        return {prefix + up: TensorSpec((I, H)), prefix + down: TensorSpec((H, I))}
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        if p["activation"] not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {p['activation']!r} is not known; known: {sorted(ops.ACTIVATIONS)}")
+        self.act = p["activation"]
+        up, down = p["names"]
+        self.w_up = tensors.get(prefix + up, env.dtype)
+        self.w_down = tensors.get(prefix + down, env.dtype)
+
+    def forward(self, x, batch):
+        return ops.linear(ops.activation(ops.linear(x, self.w_up), self.act), self.w_down)
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("dense_mlp", DenseMLP)

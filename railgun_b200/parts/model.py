@@ -18,6 +18,7 @@ from .spec import BuildEnv, ModelSpec
 from . import attention as _attention, block as _block, embedding as _embedding  # noqa: F401
 from . import mlp as _mlp, norm as _norm, rope as _rope  # noqa: F401
 from . import latent_attention as _latent_attention, moe as _moe  # noqa: F401
+from . import talking_attention as _talking_attention, recurrent as _recurrent, parallel as _parallel  # noqa: F401
 
 
 def _part_registry(role: str):
@@ -34,6 +35,7 @@ def expected_tensors(spec: ModelSpec) -> dict:
             if b.post_norm is not None:
                 out.update(NORMS.get(b.post_norm.kind).tensor_specs(b.post_norm.params, layer.prefix))
             out.update(_part_registry(b.role).get(b.part.kind).tensor_specs(b.part.params, layer.prefix))
+            out.update(ARRANGEMENTS.get(layer.arrangement).tensor_specs(b, layer.prefix))
     for op in spec.stream_ops:
         out.update(STREAM_OPS.get(op.kind).tensor_specs(op.params, ""))
     out.update(NORMS.get(spec.final_norm.kind).tensor_specs(spec.final_norm.params, ""))
@@ -80,6 +82,7 @@ class Branch:
     part: object
     role: str                       # "mixer" or "ffn"
     post_norm: object = None
+    wiring: object = None           # what the arrangement built for this branch (``Arrangement.bind``)
 
 
 @dataclass
@@ -116,6 +119,8 @@ class DecoderModel:
                                  if b.post_norm is not None else None) for b in ls.branches()],
                 arrangement=ARRANGEMENTS.get(ls.arrangement)(),
             ))
+            for built, b in zip(self.layers[-1].branches, ls.branches()):
+                built.wiring = self.layers[-1].arrangement.bind(b, ls.prefix, env, tensors)
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, "", env, tensors)
         self.head = HEADS.get(spec.head.kind)(spec.head.params, "", env, tensors)
         self.stream_ops = [STREAM_OPS.get(op.kind)(op.params, "", env, tensors) for op in spec.stream_ops]
@@ -162,7 +167,8 @@ class DecoderModel:
                                  for b in self.spec.layers[layer_index].branches() if b.role == "mixer") if n is not None]
             if len(found) > 1:
                 raise ValueError(f"layer {layer_index} has {len(found)} mixers that keep something between steps; "
-                                 "a layer's schedule entry names one cache")
+                                 "a layer's schedule entry names one cache (a mixer that keeps several things "
+                                 "asks for them as one tuple of needs)")
             return found[0] if found else None
 
         needs = {}
@@ -189,5 +195,6 @@ class DecoderModel:
             layer.arrangement.run(layer, stream, batch, cache.view(e.cache), e.writes)
         if batch.num_wanted == 0:
             return None
+        stream.close()
         h = normed_input(self.final_norm, None, stream, rows=batch.want_rows)
         return self.head.logits(h)

@@ -29,6 +29,11 @@ class SubLayer:
     part: PartSpec
     role: str                       # "mixer" or "ffn"
     post_norm: PartSpec | None = None   # a norm on the part's output, for arrangements that have one
+    wiring: dict | None = None          # what the arrangement needs to know about this branch (tensor names, counts)
+
+    def __hash__(self):
+        return hash((self.norm, self.part, self.role, self.post_norm,
+                     repr(sorted(self.wiring.items())) if self.wiring else None))
 
     def __post_init__(self):
         if self.role not in ("mixer", "ffn"):
@@ -81,6 +86,28 @@ class ScheduleEntry:
     cache: int
     writes: bool = True
     before: int = -1
+
+
+def looped_run_order(n_layers: int, loop, before: int = -1) -> tuple:
+    """Schedule entries for layers of which a span runs several times in a row:
+    the layers before the span, the span ``loop.times`` times (every pass with
+    caches of its own; its first layer behind stream operation ``before``, if
+    one is named), the layers after it.  ``loop``: None, or anything with
+    ``start``, ``stop`` and ``times``."""
+    if loop is None:
+        return tuple(ScheduleEntry(i, i) for i in range(n_layers))
+    order, cache = [], 0
+    for i in range(loop.start):
+        order.append(ScheduleEntry(i, cache))
+        cache += 1
+    for _ in range(loop.times):
+        for i in range(loop.start, loop.stop):
+            order.append(ScheduleEntry(i, cache, True, before if i == loop.start else -1))
+            cache += 1
+    for i in range(loop.stop, n_layers):
+        order.append(ScheduleEntry(i, cache))
+        cache += 1
+    return tuple(order)
 
 
 @dataclass(frozen=True)

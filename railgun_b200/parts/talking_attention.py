@@ -1,0 +1,96 @@
+"""Grouped-query attention whose heads talk before the softmax.
+
+q, k, v = x Wq^T, x Wk^T, x Wv^T; every q and k head is RMS-normed over its
+own numbers with one weight vector shared by the heads (one for q, one for
+k), then the first ``rot_dims`` numbers of each are rotated in pairs
+(i, i + rot_dims/2); the scaled scores of all heads for one (query, key) pair
+are mixed by a matrix M [heads, heads], s'_h = sum_g M[h, g] s_g, before each
+head's softmax; values may have another size than keys.  One cache row per
+token holds all key heads, then all value heads.
+
+Sizes and constants are parameters; the norm and the mixing can be left out,
+which gives plain grouped-query attention with separate key and value sizes.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..cache.manager import PagedKVNeed
+from ..weights.loader import TensorSpec
+from .base import Mixer
+from .latent_attention import rotary_frequencies
+from .registry import register_mixer
+
+
+class TalkingAttention(Mixer):
+    """params: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``
+    (query/key numbers per head), ``v_dim``, ``scale``, ``rot_dims``,
+    ``rot_base``, ``eps`` (of the q and k norms), ``window`` (0: none),
+    ``base`` (what the tensor names start with after the prefix, default
+    "mix."; the tensors are q, k, v, o, q.norm, k.norm, talk), ``qk_norm`` and
+    ``talk`` (default true: false leaves the mechanism and its tensor out)."""
+
+    @classmethod
+    def _base(cls, p, prefix):
+        return prefix + (p.get("base") if p.get("base") is not None else "mix.")
+
+    @classmethod
+    def tensor_specs(cls, p, prefix):
+        W, H, G, d, dv = p["hidden_size"], p["num_heads"], p["num_kv_heads"], p["head_dim"], p["v_dim"]
+        b = cls._base(p, prefix)
+        out = {b + "q": TensorSpec((H * d, W)), b + "k": TensorSpec((G * d, W)), b + "v": TensorSpec((G * dv, W)),
+               b + "o": TensorSpec((W, H * dv))}
+        if p.get("qk_norm", True):
+            out[b + "q.norm"] = TensorSpec((d,), init="norm")
+            out[b + "k.norm"] = TensorSpec((d,), init="norm")
+        if p.get("talk", True):
+            out[b + "talk"] = TensorSpec((H, H), init="eye")
+        return out
+
+    @classmethod
+    def cache_need(cls, p):
+        G, d, dv = p["num_kv_heads"], p["head_dim"], p["v_dim"]
+        return PagedKVNeed(G, d + dv, int(p.get("window") or 0), page_shape=("page", G * (d + dv)))
+
+    def __init__(self, p, prefix, env, tensors):
+        super().__init__(p, prefix, env, tensors)
+        self.H, self.G, self.d, self.dv = p["num_heads"], p["num_kv_heads"], p["head_dim"], p["v_dim"]
+        if self.H % self.G:
+            raise ValueError(f"{self.H} heads cannot share {self.G} key/value heads")
+        self.rot_dims = int(p.get("rot_dims") or 0)
+        if self.rot_dims % 2 or not 0 <= self.rot_dims <= self.d:
+            raise ValueError(f"{self.rot_dims} rotated numbers do not fit a head of {self.d}")
+        self.window = int(p.get("window") or 0)
+        self.scale = float(p["scale"]) if p.get("scale") is not None else float(self.d) ** -0.5
+        self.eps = float(p.get("eps") or 0.0)
+        b = self._base(p, prefix)
+        self.w_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in ("q", "k", "v")], dim=0).contiguous()
+        tensors.drop(b + "q", b + "k", b + "v")
+        self.w_o = tensors.get(b + "o", env.dtype)
+        self.out_features = self.H * self.dv
+        norm = p.get("qk_norm", True)
+        self.q_norm = tensors.get(b + "q.norm", torch.float32).contiguous() if norm else None
+        self.k_norm = tensors.get(b + "k.norm", torch.float32).contiguous() if norm else None
+        self.talk = tensors.get(b + "talk", torch.float32).contiguous() if p.get("talk", True) else None
+        base = float(p.get("rot_base") or 10000.0)
+        self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
+                                        lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
+
+    def mix(self, x, batch, cache, writes=True, out=None, out_scale: float = 1.0):
+        """The heads' outputs [T, heads * v_dim] times ``out_scale``, before the output product (into ``out``, a
+        view whose rows may be further apart, if given)."""
+        H, G, d, dv = self.H, self.G, self.d, self.dv
+        qkv = ops.linear(x, self.w_qkv)
+        q = torch.empty((qkv.shape[0], H, d), dtype=qkv.dtype, device=qkv.device)
+        slots = batch.slot_mapping[cache.group] if writes else None
+        ops.talking_prepare(qkv, q, cache.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
+                            batch.positions, slots, H, G, d, dv)
+        return ops.talking_attention_general(q, cache.kv, self.talk, batch.block_table[cache.group], batch.req_of_token,
+                                             batch.positions, G, dv, self.window, self.scale, out, out_scale)
+
+    def forward(self, x, batch, cache, writes=True):
+        return ops.linear(self.mix(x, batch, cache, writes), self.w_o)
+
+
+register_mixer("talking_attention", TalkingAttention)

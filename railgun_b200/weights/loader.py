@@ -30,7 +30,7 @@ class WeightError(ValueError):
 @dataclass(frozen=True)
 class TensorSpec:
     shape: tuple
-    init: str = "normal"        # how random-weights mode fills it: "normal" | "norm" | "zeros"
+    init: str = "normal"        # how random-weights mode fills it: "normal" | "norm" | "eye" | "zeros"
     optional: bool = False
 
 

@@ -2,7 +2,8 @@
 
 Every tensor is drawn from its own generator, seeded by the seed and a hash of
 the tensor's name, so the values do not depend on the order tensors are made
-in.  Matrices and embeddings ~ N(0, 0.02); norm weights 1 + U(-0.1, 0.1).
+in.  Matrices and embeddings ~ N(0, 0.02); norm weights 1 + U(-0.1, 0.1); small
+mixing matrices the identity + U(-0.05, 0.05).
 The reference has no such mode; its loader only reads files
 (crates/vllm-models/src/llama/model.rs:92-137).
 """
@@ -30,6 +31,9 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype=torch.bfloat16, 
         t = torch.empty(spec.shape, dtype=torch.float32).normal_(0.0, std, generator=g)
     elif spec.init == "norm":
         t = 1.0 + (torch.rand(spec.shape, dtype=torch.float32, generator=g) * 0.2 - 0.1)
+    elif spec.init == "eye":
+        t = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32) + (
+            torch.rand(spec.shape, dtype=torch.float32, generator=g) * 0.1 - 0.05)
     elif spec.init == "zeros":
         t = torch.zeros(spec.shape, dtype=torch.float32)
     else:
