@@ -158,7 +158,7 @@ def causal_conv(x, taps, bias):
     T, C = x.shape
     K = taps.shape[1]
     y = np.tile(bias, (T, 1)).astype(np.float64)
-    for k in range(K):
+    for k in range(min(K, T)):
         y[k:] += x[:T - k] * taps[:, K - 1 - k]
     return y
 
