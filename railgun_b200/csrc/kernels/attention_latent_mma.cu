@@ -34,7 +34,8 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
         const bf16* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
         const int* __restrict__ tiles, int sub, int tt, const int* __restrict__ rows_list,
         const int* __restrict__ req_of_token, const int* __restrict__ positions, int H, int hc, int R, int D,
-        int page_size, int window, float scale_log2, int nsplit) {
+        int page_size, int window, float scale_log2, int nsplit, const float* __restrict__ sink, int sel_dv, int sel_hpg,
+        int out_ld, float out_scale) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int GT = 32 * CW;                                    // threads of a row group
     constexpr int KW = LM_BN / CW;                                 // keys a warp scores per tile: 16 or 8
@@ -255,7 +256,30 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
 #pragma unroll
     for (int c = 0; c < CW; ++c) { l0 += sLw[c * 16 + g]; l1 += sLw[c * 16 + g + 8]; }
     if (nsplit == 1) {
-        const float inv0 = l0 > 0.f ? 1.f / l0 : 0.f, inv1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        if (sink) {                                                // exp(sink[head]) joins the denominator, once
+            if (ok0 && m0 > -INFINITY) l0 += ex2(sink[hd0] * 1.4426950408889634f - m0);
+            if (ok1 && m1 > -INFINITY) l1 += ex2(sink[hd1] * 1.4426950408889634f - m1);
+        }
+        const float inv0 = l0 > 0.f ? out_scale / l0 : 0.f, inv1 = l1 > 0.f ? out_scale / l1 : 0.f;
+        if (sel_dv > 0) {
+            // head h keeps columns [(h / sel_hpg) sel_dv, + sel_dv) of the R, as out[token, h sel_dv + c]
+            const int lo0 = (hd0 / sel_hpg) * sel_dv, lo1 = (hd1 / sel_hpg) * sel_dv;
+            bf16* o0 = out + (size_t)tok0 * out_ld + (size_t)hd0 * sel_dv - lo0;
+            bf16* o1 = out + (size_t)tok1 * out_ld + (size_t)hd1 * sel_dv - lo1;
+#pragma unroll
+            for (int i = 0; i < NDH; ++i) {
+                if (i < 2 * nd2) {
+                    const int col = c0 + i * 8 + tq * 2;
+                    if (ok0 && col >= lo0 && col < lo0 + sel_dv) {
+                        o0[col] = __float2bfloat16_rn(o[i][0] * inv0); o0[col + 1] = __float2bfloat16_rn(o[i][1] * inv0);
+                    }
+                    if (ok1 && col >= lo1 && col < lo1 + sel_dv) {
+                        o1[col] = __float2bfloat16_rn(o[i][2] * inv1); o1[col + 1] = __float2bfloat16_rn(o[i][3] * inv1);
+                    }
+                }
+            }
+            return;
+        }
         bf16* o0 = out + ((size_t)tok0 * H + hd0) * R + c0;
         bf16* o1 = out + ((size_t)tok1 * H + hd1) * R + c0;
 #pragma unroll
@@ -285,7 +309,8 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
 
 // out[token, head] = sum_z 2^(m_z - M) o_z / sum_z 2^(m_z - M) l_z over the shares that saw keys, in share order
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    bf16* __restrict__ out, const int* __restrict__ rows_list, int H, int R, int nsplit) {
+                                    bf16* __restrict__ out, const int* __restrict__ rows_list, int H, int R, int nsplit,
+                                    const float* __restrict__ sink, int sel_dv, int sel_hpg, int out_ld, float out_scale) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float wz[];                  // a share's factor 2^(m_z - M) / L, 0 for a share without keys
@@ -304,21 +329,28 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
             L += l * f;
         }
         L = warp_sum(L);
-        const float inv = L > 0.f ? 1.f / L : 0.f;
+        if (sink && M > -INFINITY) L += ex2(sink[h] * 1.4426950408889634f - M);
+        const float inv = L > 0.f ? out_scale / L : 0.f;
         for (int z = threadIdx.x; z < nsplit; z += 32) wz[z] *= inv;
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+    const int first = sel_dv > 0 ? (h / sel_hpg) * sel_dv : 0, count = sel_dv > 0 ? sel_dv : R;
+    bf16* orow = sel_dv > 0 ? out + (size_t)t * out_ld + (size_t)h * sel_dv : out + ((size_t)t * H + h) * R;
+    for (int c = threadIdx.x; c < count; c += blockDim.x) {
         float acc = 0.f;
 #pragma unroll 4
         for (int z = 0; z < nsplit; ++z) {
             const float f = wz[z];
-            if (f > 0.f) acc += part_o[(base + z) * R + c] * f;
+            if (f > 0.f) acc += part_o[(base + z) * R + first + c] * f;
         }
-        out[((size_t)t * H + h) * R + c] = __float2bfloat16_rn(acc);
+        orow[c] = __float2bfloat16_rn(acc);
     }
 }
 
+// Options of both kernels: `sink` [H] (exp(sink[h]) joins head h's denominator once: in the kernel without
+// shares, in the merge with them); `sel_dv` > 0: head h keeps only columns [(h / sel_hpg) sel_dv, + sel_dv) of
+// its R output numbers and writes them to out[token * out_ld + h * sel_dv + c] (a cache row that holds several
+// value heads side by side, of which a head wants its own); `out_scale` multiplies the result.
 template <typename K> static int lm_allow_smem(K kernel, size_t bytes) {
     return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
@@ -341,8 +373,11 @@ extern "C" int rg_latent_attention_mma_ok(int H, int R, int D) {
 extern "C" int rg_latent_attention_mma(
         const void* qa, void* out, float* part_o, float* part_ml, const void* cache, const int* block_table,
         int max_blocks, const int* tiles, const int* rows_list, int n_items, const int* req_of_token,
-        const int* positions, int H, int R, int D, int page_size, int window, float scale, int nsplit, void* stream) {
+        const int* positions, int H, int R, int D, int page_size, int window, float scale, int nsplit,
+        const float* sink, int sel_dv, int sel_hpg, int out_ld, float out_scale, void* stream) {
     if (n_items <= 0) return 0;
+    if (sel_dv < 0 || (sel_dv > 0 && (sel_hpg < 1 || (sel_dv & 1) || ((H + sel_hpg - 1) / sel_hpg) * sel_dv > R)))
+        return RG_ERR_UNSUPPORTED;
     if (rg_latent_attention_mma_ok(H, R, D) || page_size < 1 || nsplit < 1 || nsplit > 65535) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     const int hc = H < 64 ? H : 64, chunks = (H + hc - 1) / hc;
@@ -365,11 +400,11 @@ extern "C" int rg_latent_attention_mma(
 #define RG_LM(N, C) { e = lm_allow_smem(latent_attention_mma_kernel<N, C>, smem); if (e) return e; \
         e = rg_launch(latent_attention_mma_kernel<N, C>, grid, block, smem, s, 1, (const bf16*)qa, (bf16*)out, part_o, part_ml, \
                       (const bf16*)cache, block_table, max_blocks, tiles, sub, tt, rows_list, req_of_token, positions, H, hc, \
-                      R, D, page_size, window, scale_log2, nsplit); }
+                      R, D, page_size, window, scale_log2, nsplit, sink, sel_dv, sel_hpg, out_ld, out_scale); }
     if (CW == 2) { if (ndh <= 8) RG_LM(8, 2) else if (ndh <= 16) RG_LM(16, 2) else RG_LM(32, 2) }
     else { if (ndh <= 4) RG_LM(4, 4) else if (ndh <= 8) RG_LM(8, 4) else RG_LM(16, 4) }
 #undef RG_LM
     if (e || nsplit == 1) return e;
     return rg_launch(latent_merge_kernel, dim3(n_items, H), dim3(R >= 256 ? 128 : 64), (size_t)nsplit * sizeof(float), s, 1, (const float*)part_o,
-                     (const float*)part_ml, (bf16*)out, rows_list, H, R, nsplit);
+                     (const float*)part_ml, (bf16*)out, rows_list, H, R, nsplit, sink, sel_dv, sel_hpg, out_ld, out_scale);
 }

@@ -9,11 +9,19 @@
 //   out_h[i]   = sum_j p_h[i, j] v_kv(h)[j]
 // All of it 32-bit; the cache and the outputs are in the storage type.
 //
-// Cache layout: one row per token, [pages * page_size, G * d + G * dv] = all key heads, then all value heads.
+// Cache layout: one row per token, [pages * page_size, G * dv + G * d] = all value heads, then all key heads.
 //
 // Kernels here:
 //   talking_prepare             per token: norm and rotation of q (into q_out [T, H, d]) and k, cache row write
 //   talking_attention_general   one block per token, all heads together, any sizes with H * dv <= 4096
+//
+// On the tensor cores the mixing moves into the queries, where it is linear: with the keys of all G key/value
+// heads side by side, K_j = [k_0[j] | ... | k_(G-1)[j]], and
+//   Q'_h = [ scale sum_{g in group 0} M[h, g] q_g | ... | scale sum_{g in group G-1} M[h, g] q_g ]   (G d numbers)
+// the mixed score is s'_h[i, j] = Q'_h[i] . K_j: every head attends to the same rows, as in attention over a
+// latent cache, and that kernel (attention_latent_mma.cu) runs it: its queries are [0 (G dv) | Q'_h], its
+// scores run over the whole cache row [V | K], its values are the row's first G dv numbers, of which head h
+// keeps the dv of its own key/value head.  talking_prepare writes those queries when asked (qa).
 #include "common.cuh"
 
 #define TK_THREADS 128
@@ -25,9 +33,10 @@ template <typename A>
 __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __restrict__ q_out, A* __restrict__ cache,
                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                                        const double* __restrict__ freq, int dims, const int* __restrict__ positions,
-                                       const int* __restrict__ slots, int H, int G, int d, int dv) {
+                                       const int* __restrict__ slots, int H, int G, int d, int dv,
+                                       A* __restrict__ qa, const float* __restrict__ talk, float scale) {
     extern __shared__ float sm[];                    // cos | sin of the token's dims / 2 angles, then one head's numbers per warp
-    float* cs = sm;
+    float* cs = sm;                                  // (and, for qa, all heads' rotated queries behind them)
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
@@ -42,6 +51,7 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     float* buf = sm + dims + warp * d;
+    float* qall = sm + dims + nwarp * d;             // [H * d], only with qa
     const A* row = qkv + (size_t)t * ld;
     const int slot = slots ? slots[t] : -1;
     const int rowlen = G * (d + dv);
@@ -56,36 +66,59 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
         ss = warp_sum(ss);
         const float inv = w ? rsqrtf(ss / (float)d + eps) : 1.f;
         __syncwarp();
-        A* dst = is_q ? q_out + ((size_t)t * H + hh) * d : cache + (size_t)slot * rowlen + (size_t)(hh - H) * d;
+        A* dst = is_q ? (q_out ? q_out + ((size_t)t * H + hh) * d : nullptr)
+                      : cache + (size_t)slot * rowlen + (size_t)G * dv + (size_t)(hh - H) * d;
         for (int i = lane; i < d; i += 32) {
             const float wi = w ? w[i] : 1.f;
             float v = buf[i] * inv * wi;
             if (i < half) v = v * cs[i] - buf[i + half] * inv * (w ? w[i + half] : 1.f) * cs[half + i];
             else if (i < dims) v = v * cs[i - half] + buf[i - half] * inv * (w ? w[i - half] : 1.f) * cs[i];
-            dst[i] = from_f32<A>(v);
+            if (dst) dst[i] = from_f32<A>(v);
+            if (is_q && qa) qall[hh * d + i] = v;
         }
         __syncwarp();
     }
-    if (slot < 0) return;
-    const A* vsrc = row + (size_t)(H + G) * d;
-    A* vdst = cache + (size_t)slot * rowlen + (size_t)G * d;
-    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) vdst[i] = vsrc[i];
+    if (slot >= 0) {
+        const A* vsrc = row + (size_t)(H + G) * d;
+        A* vdst = cache + (size_t)slot * rowlen;
+        for (int i = threadIdx.x; i < G * dv; i += blockDim.x) vdst[i] = vsrc[i];
+    }
+    if (!qa) return;
+    // the queries of the tensor-core form: [0 (G dv) | for every key/value head c: scale sum_{g in c} M[h, g] q_g]
+    __syncthreads();
+    const int hpg = H / G, Dq = G * (d + dv);
+    A* qrow = qa + (size_t)t * H * Dq;
+    for (int e = threadIdx.x; e < H * Dq; e += blockDim.x) {
+        const int h = e / Dq, j = e - h * Dq;
+        float v = 0.f;
+        if (j >= G * dv) {
+            const int c = (j - G * dv) / d, i = (j - G * dv) - c * d;
+            if (talk) { for (int g = c * hpg; g < (c + 1) * hpg; ++g) v += talk[h * H + g] * qall[g * d + i]; }
+            else if (h / hpg == c) v = qall[h * d + i];
+            v *= scale;
+        }
+        qrow[e] = from_f32<A>(v);
+    }
 }
 
 extern "C" int rg_talking_prepare(const void* qkv, int dtype, int ld, void* q_out, void* cache, const float* q_norm,
                                   const float* k_norm, float eps, const double* freq, int dims, const int* positions,
-                                  const int* slots, int T, int H, int G, int d, int dv, void* stream) {
+                                  const int* slots, int T, int H, int G, int d, int dv, void* qa, const float* talk,
+                                  float scale, void* stream) {
     if (T <= 0) return 0;
-    if (dims < 0 || dims > d || (dims & 1) || H < 1 || G < 1 || d < 1 || dv < 1) return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d) * sizeof(float);
+    if (dims < 0 || dims > d || (dims & 1) || H < 1 || G < 1 || H % G || d < 1 || dv < 1 || (!q_out && !qa))
+        return RG_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d + (qa ? H * d : 0)) * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(talking_prepare_kernel<bf16>, dim3(T), dim3(TK_THREADS), smem, s, 1, (const bf16*)qkv, ld,
-                         (bf16*)q_out, (bf16*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv);
+                         (bf16*)q_out, (bf16*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv,
+                         (bf16*)qa, talk, scale);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(talking_prepare_kernel<float>, dim3(T), dim3(TK_THREADS), smem, s, 1, (const float*)qkv, ld,
-                         (float*)q_out, (float*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv);
+                         (float*)q_out, (float*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv,
+                         (float*)qa, talk, scale);
     return RG_ERR_UNSUPPORTED;
 }
 
@@ -124,7 +157,7 @@ __global__ void talking_attention_general_kernel(
         const int e = threadIdx.x + k * TK_THREADS;
         const int h = e < H * dv ? e / dv : 0;
         acc_h[k] = e < H * dv ? h : -1;
-        acc_off[k] = G * d + (h / hpg) * dv + (e - h * dv);
+        acc_off[k] = (h / hpg) * dv + (e - h * dv);
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -136,7 +169,7 @@ __global__ void talking_attention_general_kernel(
             srow[threadIdx.x] = row;
             const A* krow = cache + (size_t)row * rowlen;
             for (int g = 0; g < H; ++g) {
-                const A* kh = krow + (g / hpg) * d;
+                const A* kh = krow + G * dv + (g / hpg) * d;
                 const float* qh = qs + g * d;
                 float dot = 0.f;
                 for (int i = 0; i < d; ++i) dot += qh[i] * to_f32(kh[i]);

@@ -327,18 +327,36 @@ def latent_decode_splits(n_tokens: int, head_chunks: int, max_context: int) -> i
 
 def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tiles,
                          rows, n_items: int, req_of_token: torch.Tensor, positions: torch.Tensor, R: int, window: int,
-                         scale: float, num_splits: int = 1) -> None:
+                         scale: float, num_splits: int = 1, sink: torch.Tensor | None = None, select=None,
+                         out_scale: float = 1.0) -> None:
     """Attention over the latent cache on the tensor cores, into ``out`` [T, H, R].  With ``tiles`` [n, 3]
     (first row, rows <= 64, request): requests with several tokens.  Without: ``n_items`` single tokens
-    (``rows``, or rows 0..n_items-1), every context cut into ``num_splits`` shares that a second kernel adds."""
+    (``rows``, or rows 0..n_items-1), every context cut into ``num_splits`` shares that a second kernel adds.
+    ``sink`` [H] float32: exp(sink[h]) joins head h's denominator.  ``select`` = (dv, heads per group): head h
+    keeps only columns [(h // heads per group) dv, + dv) of its R output numbers, and ``out`` is a [T, H dv] view
+    (rows may be further apart).  ``out_scale`` multiplies the result."""
     _check(qa, "qa", torch.bfloat16)
-    _check(out, "out", torch.bfloat16)
     _check(cache, "cache", torch.bfloat16)
     _check(block_table, "block_table", torch.int32)
     _check(req_of_token, "req_of_token", torch.int32)
     _check(positions, "positions", torch.int32)
     T, H, D = qa.shape
-    if cache.dim() != 3 or cache.shape[2] != D or out.shape != (T, H, R) or not latent_attention_mma_ok(qa.dtype, H, R, D):
+    sel_dv, sel_hpg, out_ld = 0, 1, 0
+    if select is not None:
+        sel_dv, sel_hpg = int(select[0]), int(select[1])
+        _check_out_view(out, T, H * sel_dv, torch.bfloat16, "latent_attention_mma")
+        out_ld = out.stride(0)
+        if sel_dv < 2 or sel_dv % 2 or sel_hpg < 1 or -(-H // sel_hpg) * sel_dv > R:
+            raise KernelError(f"latent_attention_mma: cannot select {sel_dv} of {R} columns per group of {sel_hpg} heads")
+    else:
+        _check(out, "out", torch.bfloat16)
+        if out.shape != (T, H, R):
+            raise KernelError(f"latent_attention_mma: out {tuple(out.shape)} is not [{T}, {H}, {R}]")
+    if sink is not None:
+        _check(sink, "sink", torch.float32)
+        if sink.numel() != H:
+            raise KernelError(f"{sink.numel()} sinks for {H} heads")
+    if cache.dim() != 3 or cache.shape[2] != D or not latent_attention_mma_ok(qa.dtype, H, R, D):
         raise KernelError(f"latent_attention_mma: queries {tuple(qa.shape)}, cache {tuple(cache.shape)}, latent {R}")
     for t, name in ((tiles, "tiles"), (rows, "rows")):
         if t is not None:
@@ -352,7 +370,7 @@ def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
         _ptr(qa), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(tiles), _ptr(rows), c_int(n_items), _ptr(req_of_token), _ptr(positions), c_int(H), c_int(R), c_int(D),
         c_int(cache.shape[1]), c_int(window or 0), c_float(scale), c_int(num_splits if tiles is None else 1),
-        _stream()), "latent_attention_mma")
+        _ptr(sink), c_int(sel_dv), c_int(sel_hpg), c_int(out_ld), c_float(out_scale), _stream()), "latent_attention_mma")
 
 
 MOE_TILE_ROWS = 32
@@ -515,18 +533,31 @@ def hyper_step(copies, x0, y, mix, outc, inc, norm_w, eps: float, out_dtype, out
     return out
 
 
-def talking_prepare(qkv: torch.Tensor, q_out: torch.Tensor, cache, q_norm, k_norm, eps: float, freq: torch.Tensor,
-                    rot_dims: int, positions: torch.Tensor, slots, H: int, G: int, d: int, dv: int) -> None:
+def talking_prepare(qkv: torch.Tensor, q_out, cache, q_norm, k_norm, eps: float, freq: torch.Tensor,
+                    rot_dims: int, positions: torch.Tensor, slots, H: int, G: int, d: int, dv: int,
+                    qa: torch.Tensor | None = None, talk=None, scale: float = 1.0) -> None:
     """Per token of ``qkv`` [T, H d + G d + G dv]: every q and k head is RMS-normed over its d numbers
     (``q_norm`` / ``k_norm`` [d] float32, None: no norm) and its first ``rot_dims`` numbers are rotated in
-    pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64); q goes to ``q_out`` [T, H, d], the keys
-    and the values to row ``slots[t]`` of ``cache`` [pages, page, G d + G dv] (negative slot or None: no write)."""
+    pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64); q goes to ``q_out`` [T, H, d] (if given),
+    the values and the keys to row ``slots[t]`` of ``cache`` [pages, page, G dv + G d] (negative slot or None: no
+    write).  ``qa`` [T, H, G dv + G d] (if given) receives the queries of the tensor-core form: zeros, then for
+    every key/value head c the numbers ``scale`` * sum over the heads g of c of ``talk``[h, g] q_g."""
     _check(qkv, "qkv")
-    _check(q_out, "q_out", qkv.dtype)
+    if q_out is None and qa is None:
+        raise KernelError("talking_prepare: nowhere to put the queries")
     _check(freq, "freq", torch.float64)
     _check(positions, "positions", torch.int32)
     T = qkv.shape[0]
-    if qkv.shape[1] != (H + G) * d + G * dv or q_out.shape != (T, H, d) or positions.numel() != T:
+    if q_out is not None:
+        _check(q_out, "q_out", qkv.dtype)
+    if qa is not None:
+        _check(qa, "qa", qkv.dtype)
+        if qa.shape != (T, H, G * (d + dv)):
+            raise KernelError(f"talking_prepare: qa {tuple(qa.shape)} is not [T, {H}, {G * (d + dv)}]")
+        if talk is not None:
+            _check(talk, "talk", torch.float32)
+    if (qkv.shape[1] != (H + G) * d + G * dv or (q_out is not None and q_out.shape != (T, H, d))
+            or positions.numel() != T):
         raise KernelError(f"talking_prepare: qkv {tuple(qkv.shape)} does not match {H} + {G} heads of {d}, values of {dv}")
     for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
         if w is not None:
@@ -545,7 +576,7 @@ def talking_prepare(qkv: torch.Tensor, q_out: torch.Tensor, cache, q_norm, k_nor
     _ok(_fn("attention_talking", "rg_talking_prepare")(
         _ptr(qkv), c_int(_dtype_code(qkv)), c_int(qkv.stride(0)), _ptr(q_out), _ptr(cache if slots is not None else None),
         _ptr(q_norm), _ptr(k_norm), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions), _ptr(slots), c_int(T),
-        c_int(H), c_int(G), c_int(d), c_int(dv), _stream()), "talking_prepare")
+        c_int(H), c_int(G), c_int(d), c_int(dv), _ptr(qa), _ptr(talk), c_float(scale), _stream()), "talking_prepare")
 
 
 def _check_out_view(out, T: int, n: int, dtype, what: str):
@@ -556,7 +587,7 @@ def _check_out_view(out, T: int, n: int, dtype, what: str):
 def talking_attention_general(q: torch.Tensor, cache: torch.Tensor, talk, block_table: torch.Tensor,
                               req_of_token: torch.Tensor, positions: torch.Tensor, G: int, dv: int, window: int,
                               scale: float, out: torch.Tensor | None = None, out_scale: float = 1.0) -> torch.Tensor:
-    """Attention of ``q`` [T, H, d] over cache rows [pages, page, G d + G dv] with the heads' scores mixed by
+    """Attention of ``q`` [T, H, d] over cache rows [pages, page, G dv + G d] (values, then keys) with the heads' scores mixed by
     ``talk`` [H, H] (float32; None: no mixing) before the softmax.  Returns [T, H dv] times ``out_scale``
     (``out``: a view to write into, rows may be further apart).  32-bit arithmetic, H dv <= 4096."""
     _check(q, "q")

@@ -177,23 +177,26 @@ class LatentAttention(Mixer):
         64 / heads tokens, single tokens with their contexts cut into shares); everything else, and all of the
         32-bit path, through the general kernel."""
         table = batch.block_table[cache.group]
-        if self.sink is not None or not ops.latent_attention_mma_ok(qa.dtype, self.H, self.R, self.D):
+        if not ops.latent_attention_mma_ok(qa.dtype, self.H, self.R, self.D):
             return ops.latent_attention_general(qa, cache.kv, table, batch.req_of_token, batch.positions, self.R,
                                                 self.window, self.scale, self.sink)
         out = torch.empty((qa.shape[0], self.H, self.R), dtype=qa.dtype, device=qa.device)
         chunks = -(-self.H // 64)
         args = (batch.req_of_token, batch.positions, self.R, self.window, self.scale)
+        # a single token sees at most its window: that is what its context is cut into shares by
+        reach = min(batch.max_context_len, self.window) if self.window else batch.max_context_len
         if batch.decode_only:
             n = batch.num_tokens
             ops.latent_attention_mma(qa, out, cache.kv, table, None, None, n, *args,
-                                     ops.latent_decode_splits(n, chunks, batch.max_context_len))
+                                     ops.latent_decode_splits(n, chunks, reach), sink=self.sink)
             return out
         if batch.num_prefill_tiles:
-            ops.latent_attention_mma(qa, out, cache.kv, table, batch.prefill_tiles, None, batch.num_prefill_tiles, *args)
+            ops.latent_attention_mma(qa, out, cache.kv, table, batch.prefill_tiles, None, batch.num_prefill_tiles, *args,
+                                     sink=self.sink)
         if batch.num_decode_rows:
             n = batch.num_decode_rows
             ops.latent_attention_mma(qa, out, cache.kv, table, None, batch.decode_rows, n, *args,
-                                     ops.latent_decode_splits(n, chunks, batch.max_context_len))
+                                     ops.latent_decode_splits(n, chunks, reach), sink=self.sink)
         return out
 
 

@@ -6,7 +6,16 @@ k), then the first ``rot_dims`` numbers of each are rotated in pairs
 (i, i + rot_dims/2); the scaled scores of all heads for one (query, key) pair
 are mixed by a matrix M [heads, heads], s'_h = sum_g M[h, g] s_g, before each
 head's softmax; values may have another size than keys.  One cache row per
-token holds all key heads, then all value heads.
+token holds all value heads, then all key heads.
+
+In bfloat16, where the sizes fit, the attention runs on the tensor cores in
+the form of attention over a latent cache: the mixing is linear in q, so the
+step mixes the queries instead of the scores (Q'_h holds, for every key/value
+head c, scale * sum over c's heads g of M[h, g] q_g), every head then scores
+the same cache rows, and the kernel of ``latent_attention`` does the rest,
+each head keeping the values of its own key/value head.  Everything else,
+and the whole 32-bit path, runs the general kernel, which mixes the scores
+themselves.
 
 Sizes and constants are parameters; the norm and the mixing can be left out,
 which gives plain grouped-query attention with separate key and value sizes.
@@ -82,12 +91,39 @@ class TalkingAttention(Mixer):
         view whose rows may be further apart, if given)."""
         H, G, d, dv = self.H, self.G, self.d, self.dv
         qkv = ops.linear(x, self.w_qkv)
-        q = torch.empty((qkv.shape[0], H, d), dtype=qkv.dtype, device=qkv.device)
+        T = qkv.shape[0]
         slots = batch.slot_mapping[cache.group] if writes else None
+        table = batch.block_table[cache.group]
+        R, D = G * dv, G * (d + dv)
+        if dv % 2 == 0 and ops.latent_attention_mma_ok(qkv.dtype, H, R, D):
+            # the tensor-core form: mixed queries over the rows [values | keys]
+            qa = torch.empty((T, H, D), dtype=qkv.dtype, device=qkv.device)
+            ops.talking_prepare(qkv, None, cache.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
+                                batch.positions, slots, H, G, d, dv, qa=qa, talk=self.talk, scale=self.scale)
+            if out is None:
+                out = torch.empty((T, H * dv), dtype=qkv.dtype, device=qkv.device)
+            args = (batch.req_of_token, batch.positions, R, self.window, 1.0)
+            more = dict(select=(dv, H // G), out_scale=out_scale)
+            reach = min(batch.max_context_len, self.window) if self.window else batch.max_context_len
+            chunks = -(-H // 64)
+            if batch.decode_only:
+                n = batch.num_tokens
+                ops.latent_attention_mma(qa, out, cache.kv, table, None, None, n, *args,
+                                         ops.latent_decode_splits(n, chunks, reach), **more)
+                return out
+            if batch.num_prefill_tiles:
+                ops.latent_attention_mma(qa, out, cache.kv, table, batch.prefill_tiles, None, batch.num_prefill_tiles,
+                                         *args, **more)
+            if batch.num_decode_rows:
+                n = batch.num_decode_rows
+                ops.latent_attention_mma(qa, out, cache.kv, table, None, batch.decode_rows, n, *args,
+                                         ops.latent_decode_splits(n, chunks, reach), **more)
+            return out
+        q = torch.empty((T, H, d), dtype=qkv.dtype, device=qkv.device)
         ops.talking_prepare(qkv, q, cache.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
                             batch.positions, slots, H, G, d, dv)
-        return ops.talking_attention_general(q, cache.kv, self.talk, batch.block_table[cache.group], batch.req_of_token,
-                                             batch.positions, G, dv, self.window, self.scale, out, out_scale)
+        return ops.talking_attention_general(q, cache.kv, self.talk, table, batch.req_of_token, batch.positions, G, dv,
+                                             self.window, self.scale, out, out_scale)
 
     def forward(self, x, batch, cache, writes=True):
         return ops.linear(self.mix(x, batch, cache, writes), self.w_o)

@@ -115,7 +115,7 @@ def test_talking_attention_kernel_alone(H, G, d, dv, page, window, dtype):
         q = torch.tensor(rng.normal(size=(H, d)), dtype=TORCH[dtype]).double()
         q[0] = (k[key, 0] * 4.0).to(TORCH[dtype]).double()                  # head 0 looks for that key
         ref = plain_talking_rows(q, k, v, talk.double(), d ** -0.5, window)
-        rows = torch.cat([k.reshape(n, G * d), v.reshape(n, G * dv)], dim=1).to(TORCH[dtype])
+        rows = torch.cat([v.reshape(n, G * dv), k.reshape(n, G * d)], dim=1).to(TORCH[dtype])        # values, then keys
         cache, table = paged(rows, page, key)
         # the last token as a single token, and as the end of a portion of 70 (whose earlier queries are random)
         for portion in (1, 70):
@@ -126,6 +126,23 @@ def test_talking_attention_kernel_alone(H, G, d, dv, page, window, dtype):
                                                 dev(torch.zeros(portion, dtype=torch.int32)), dev(positions), G, dv,
                                                 window, d ** -0.5, out_scale=0.5)
             assert rel(got[-1].view(H, dv), ref * 0.5) < (2e-5 if dtype == "float32" else 2e-2), f"key {key}"
+            if dtype == "bfloat16" and dv % 2 == 0 and ops.latent_attention_mma_ok(torch.bfloat16, H, G * dv, G * (d + dv)):
+                # the tensor-core form: the mixing inside the queries, every head over the rows [values | keys]
+                hpg = H // G
+                mixed = torch.zeros((portion, H, G * (d + dv)), dtype=torch.float64)
+                for c in range(G):
+                    mixed[:, :, G * dv + c * d:G * dv + (c + 1) * d] = d ** -0.5 * torch.einsum(
+                        "hg,tgd->thd", talk.double()[:, c * hpg:(c + 1) * hpg], qs.double()[:, c * hpg:(c + 1) * hpg])
+                qa = dev(mixed.to(torch.bfloat16))
+                for splits in ((1,) if portion > 1 else (1, 2, 5)):
+                    wide = torch.zeros((portion, H * dv + 24), dtype=torch.bfloat16, device=DEV)
+                    tiles = dev(torch.tensor([[0, 64, 0], [64, portion - 64, 0]], dtype=torch.int32)) if portion > 1 else None
+                    ops.latent_attention_mma(qa, wide[:, 8:8 + H * dv], dev(cache), dev(table), tiles, None,
+                                             2 if portion > 1 else 1,
+                                             dev(torch.zeros(portion, dtype=torch.int32)), dev(positions), G * dv, window,
+                                             1.0, splits, select=(dv, hpg), out_scale=0.5)
+                    assert rel(wide[-1, 8:8 + H * dv].view(H, dv), ref * 0.5) < 3e-2, f"key {key}, tensor cores, {splits} shares"
+                    assert float(wide[:, :8].abs().max()) == 0.0 and float(wide[:, 8 + H * dv:].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -152,9 +169,21 @@ def test_talking_prepare_alone(H, G, d, dv, dims, dtype):
     flat = cache.view(-1, G * (d + dv)).cpu()
     for t in range(T):
         if slots[t] >= 0:
-            assert rel(flat[slots[t], :G * d], k_ref[t].reshape(-1)) < tol
-            assert torch.equal(flat[slots[t], G * d:], qkv[t, (H + G) * d:])
+            assert rel(flat[slots[t], G * dv:], k_ref[t].reshape(-1)) < tol
+            assert torch.equal(flat[slots[t], :G * dv], qkv[t, (H + G) * d:])
     assert float(flat[8].abs().max()) == 0.0 and float(flat[6].abs().max()) == 0.0          # untouched rows
+    # the queries of the tensor-core form: zeros, then per key/value head the mixed and scaled queries of its heads
+    talk = rng.normal(size=(H, H))
+    qa = torch.empty((T, H, G * (d + dv)), dtype=TORCH[dtype], device=DEV)
+    ops.talking_prepare(dev(qkv), None, None, dev(qn, torch.float32), dev(kn, torch.float32), 1e-5,
+                        rotary_frequencies(dims, 300.0).to(DEV), dims, dev(pos.astype(np.int32)), None, H, G, d, dv,
+                        qa=qa, talk=dev(talk, torch.float32), scale=0.3)
+    hpg = H // G
+    ref = np.zeros((T, H, G * (d + dv)))
+    for c in range(G):
+        ref[:, :, G * dv + c * d:G * dv + (c + 1) * d] = 0.3 * np.einsum(
+            "hg,tgd->thd", talk.astype(np.float32)[:, c * hpg:(c + 1) * hpg], q_ref[:, c * hpg:(c + 1) * hpg])
+    assert rel(qa, ref) < tol and float(qa[:, :, :G * dv].abs().max()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -190,6 +219,16 @@ def test_latent_attention_with_sink_and_window_alone(H, R, dr, page, window, dty
             err = np.abs(got[-1].double().cpu().numpy() - ref.numpy()).max() / float(rows[:, :R].double().abs().max())
             assert err < (2e-5 if dtype == "float32" else 2e-2), f"key {key}"
             assert float(got[-1, 1].abs().max()) < 1e-6                                    # all weight on the sink
+            if dtype == "bfloat16" and ops.latent_attention_mma_ok(torch.bfloat16, H, R, D):
+                for splits in ((1,) if portion > 1 else (1, 3)):
+                    out = torch.empty((portion, H, R), dtype=torch.bfloat16, device=DEV)
+                    tiles = dev(torch.tensor([[0, portion, 0]], dtype=torch.int32)) if portion > 1 else None
+                    ops.latent_attention_mma(dev(qs), out, dev(cache), dev(table), tiles, None, 1,
+                                             dev(torch.zeros(portion, dtype=torch.int32)), dev(positions), R, window, 0.2,
+                                             splits, sink=dev(sink))
+                    err = np.abs(out[-1].double().cpu().numpy() - ref.numpy()).max() / float(rows[:, :R].double().abs().max())
+                    assert err < 3e-2, f"key {key}, tensor cores, {splits} shares"
+                    assert float(out[-1, 1].abs().max()) < 1e-6
 
 
 # ---- mixers alone, through the cache and the state ----------------------------------------------------
