@@ -512,6 +512,131 @@ def run_dizatar(args):
     return 0
 
 
+def rupulix_sizes(name):
+    """(Rupulix configuration, the Llama configuration of equal width, layer runs and vocabulary beside it)."""
+    def rup(width, heads, kv, d, lat_heads, dim, rot, rank, window, blocks, ff, vocab):
+        par = dict(type="parallel", mlp=dict(kind="dense", ff=ff), mixer=dict(
+            left=dict(heads=heads, kv_heads=kv, dim=d, vdim=d, rot=dict(base=10000.0, dims=d // 2), scale=d ** -0.5),
+            right=dict(width=width, blocks=blocks, conv=4), left_scale=0.5, right_scale=0.5))
+        lat = dict(type="latent_attention", mlp=dict(kind="dense", ff=ff), mixer=dict(
+            heads=lat_heads, dim=dim, rot_dim=rot, vdim=dim, kv_rank=rank, scale=(dim + rot) ** -0.5,
+            rot=dict(base=10000.0, dims=rot), mask=dict(size=window)))
+        return dict(architecture="Rupulix", width=width, vocab=vocab, norm=dict(eps=1e-6), streams=2, logit_scale=1.0,
+                    loop=dict(start=1, stop=3, times=2), layers=[par, lat, par, lat])
+
+    def llama(width, heads, kv, ff, vocab, runs):
+        return dict(architectures=["LlamaForCausalLM"], hidden_size=width, num_attention_heads=heads,
+                    num_key_value_heads=kv, head_dim=64, num_hidden_layers=runs, intermediate_size=ff, vocab_size=vocab,
+                    rope_theta=500000.0, rope_scaling=None, tie_word_embeddings=True, rms_norm_eps=1e-5,
+                    max_position_embeddings=131072, torch_dtype="bfloat16")
+
+    if name == "w2048":      # 16 heads of 128 on 2 key/value heads beside a recurrence of 2,048 in 8 blocks; 16 heads of 128 + 64 over a latent of 512, window 512
+        return rup(2048, 16, 2, 128, 16, 128, 64, 512, 512, 8, 8192, 32768), llama(2048, 32, 8, 8192, 32768, 6)
+    if name == "w1024":      # 8 heads of 64 on 2 key/value heads beside a recurrence of 1,024 in 4 blocks; 8 heads of 64 + 32 over a latent of 256, window 512
+        return rup(1024, 8, 2, 64, 8, 64, 32, 256, 512, 4, 4096, 32768), llama(1024, 16, 4, 4096, 32768, 6)
+    raise ValueError(name)
+
+
+def rupulix_decode_bytes(cfg, batch, context):
+    """Bytes a decode step has to read: every weight of every layer run, the head, and what the live requests keep
+    (a windowed layer's cache only as far back as its window)."""
+    W, V = cfg["width"], cfg["vocab"]
+    order, _ = dizatar_runs(cfg)
+    total = V * W * 2
+    for i in order:
+        L = cfg["layers"][i]
+        m = L["mixer"]
+        if L["type"] == "latent_attention":
+            H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            total += (H * (dn + dr) * W + (R + dr) * W + H * dn * R + H * dv * R + W * H * dv) * 2
+            total += batch * min(context, (m.get("mask") or {}).get("size", context)) * (R + dr) * 2
+        else:
+            a, r = m["left"], m["right"]
+            H, G, d, dv, C, B = a["heads"], a["kv_heads"], a["dim"], a["vdim"], r["width"], r["blocks"]
+            total += ((H + G) * d * W + G * dv * W + W * H * dv + 3 * C * W) * 2 + 2 * C * (C // B) * 4
+            total += batch * (context * G * (d + dv) * 2 + r["conv"] * C * 4)
+        if L["mlp"]:
+            total += 2 * L["mlp"]["ff"] * W * 2
+    return total
+
+
+def rupulix_prefill_flops(cfg, T):
+    """FLOPs of one prompt of T tokens by the design's own arithmetic: products, attention over the keys a query
+    sees (the latent layers in the absorbed form the engine runs), the heads' score mixing, the gates."""
+    W, V = cfg["width"], cfg["vocab"]
+    order, _ = dizatar_runs(cfg)
+    total = 2 * V * W
+    for i in order:
+        L = cfg["layers"][i]
+        m = L["mixer"]
+        if L["type"] == "latent_attention":
+            H, dn, dr, dv, R = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            win = (m.get("mask") or {}).get("size", T)
+            pairs = sum(min(t + 1, win) for t in range(T))
+            total += 2 * T * (H * (dn + dr) * W + (R + dr) * W + H * dn * R + H * dv * R + W * H * dv)
+            total += H * 2 * (2 * R + dr) * pairs
+        else:
+            a, r = m["left"], m["right"]
+            H, G, d, dv, C, B = a["heads"], a["kv_heads"], a["dim"], a["vdim"], r["width"], r["blocks"]
+            total += 2 * T * ((H + G) * d * W + G * dv * W + W * H * dv + 3 * C * W + 2 * C * (C // B))
+            total += (H * 2 * (d + dv) + 2 * H * H) * (T * (T + 1) // 2)
+        if L["mlp"]:
+            total += 2 * T * 2 * L["mlp"]["ff"] * W
+    return total
+
+
+def run_rupulix(args):
+    """Prefill and decode throughput of Rupulix at layer sizes of real models (random weights), beside the dense
+    GQA Llama of equal width, number of layer runs and vocabulary.  One JSON line per model and size."""
+    import numpy as np
+    import torch
+    from railgun_b200.engine.batch import StepEntry
+    from railgun_b200.engine.engine import Engine
+    page, pool_tokens = 16, 64 * 4096
+    pk, pk_src = peaks()
+    for size in (args.sizes.split(",") if args.sizes else ["w1024", "w2048"]):
+        for label, cfg in zip(("rupulix", "llama"), rupulix_sizes(size)):
+            mdir = model_folder(cfg)
+            eng = Engine(mdir, dtype="bfloat16", block_size=page, num_gpu_blocks=pool_tokens // page, max_num_seqs=64,
+                         max_num_batched_tokens=8192, max_model_len=4096)
+            runner = eng.runner
+            V = cfg.get("vocab", cfg.get("vocab_size"))
+            rng = np.random.default_rng(0)
+            _, _, time_decode = decode_tools(runner, V, rng)
+            line = {"mode": "rupulix", "size": size, "model": label, "layer_runs": len(runner.model.order),
+                    "cache_bytes_per_token": runner.cache.bytes_per_token()}
+            for b in (8, 64):
+                tok_s, ms, n_launch, _ = time_decode(b, args.steps, args.warmup, 1000 * b, args.context)
+                line[f"decode_b{b}_tok_s"], line[f"decode_b{b}_ms"] = round(tok_s, 1), round(ms, 4)
+                line[f"decode_b{b}_launches_per_step"] = n_launch // args.steps
+                ctx = args.context + args.warmup + args.steps // 2
+                by = (rupulix_decode_bytes(cfg, b, ctx) if label == "rupulix"
+                      else decode_bytes(cfg, b, ctx, runner.cache.bytes_per_token()))
+                line[f"decode_b{b}_GB_per_step"] = round(by / 1e9, 3)
+                line[f"decode_b{b}_frac_hbm"] = round(by / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 3)
+            prompt = rng.integers(0, V, size=args.tokens).tolist()
+            times = []
+            for i in range(args.warmup + 7):
+                torch.cuda.synchronize()
+                t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                t0.record()
+                runner.step([StepEntry(7000 + i, prompt, [args.tokens - 1])])
+                t1.record()
+                torch.cuda.synchronize()
+                runner.end([7000 + i])
+                times.append(t0.elapsed_time(t1))
+            runner.check_device_errors()
+            ms = sorted(times[args.warmup:])[len(times[args.warmup:]) // 2]
+            fl = rupulix_prefill_flops(cfg, args.tokens) if label == "rupulix" else prefill_flops(cfg, args.tokens)
+            line.update(prefill_tokens=args.tokens, prefill_ms=round(ms, 3), prefill_tok_s=round(args.tokens / ms * 1e3, 1),
+                        prefill_TFLOP=round(fl / 1e12, 3), prefill_frac_flops=round(fl / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                        peaks=pk_src)
+            print(json.dumps(line), flush=True)
+            del eng, runner, time_decode
+            torch.cuda.empty_cache()
+    return 0
+
+
 def run_kernels(args):
     """Times the hot kernels one by one, each as a CUDA graph of 16 calls over 16 different operand sets (so
     that weights and caches come from HBM, not L2), with CUDA events around replays.  One JSON line per case."""
@@ -739,11 +864,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the named configuration (0: all)")
-    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar"],
+    ap.add_argument("--mode", default="all", choices=["all", "decode", "prefill", "kernels", "dizatar", "rupulix"],
                     help="all: the contract's line; decode / prefill: one short measurement (for profiling); "
-                         "kernels: the hot kernels one by one; dizatar: prefill and decode of the Dizatar design at "
+                         "kernels: the hot kernels one by one; dizatar / rupulix: prefill and decode of the Dizatar / Rupulix design at "
                          "layer sizes of real models beside the dense model of equal width")
-    ap.add_argument("--sizes", default="", help="--mode dizatar: comma-separated subset of w1024, w2048")
+    ap.add_argument("--sizes", default="", help="--mode dizatar / rupulix: comma-separated subset of w1024, w2048")
     ap.add_argument("--cases", default="", help="--mode kernels: comma-separated subset of sampling, decode_gemm, "
                     "decode_gemm_mid, decode_attention, prefill_gemm, prefill_attention, primitives, latent_attention, moe")
     ap.add_argument("--batch", type=int, default=8, help="--mode decode: requests in the batch")
@@ -764,6 +889,8 @@ def main():
         return run_kernels(args)
     if args.mode == "dizatar":
         return run_dizatar(args)
+    if args.mode == "rupulix":
+        return run_rupulix(args)
     return run_ours(args)
 
 

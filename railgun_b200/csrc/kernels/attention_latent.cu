@@ -63,12 +63,8 @@ __global__ void latent_rope_cache_kernel(const A* __restrict__ proj, int ld, int
     const double pos = (double)positions[t];
     const A* row = proj + (size_t)t * ld;
     const int D = R + dr;
-    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {      // angles in 64-bit: a handful per token
-        double sn, c;
-        sincos(pos * freq[i], &sn, &c);
-        cs[i] = (float)c;
-        cs[(rot_dims >> 1) + i] = (float)sn;
-    }
+    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x)        // angles in 64-bit: a handful per token
+        rotary_cos_sin(pos, freq[i], &cs[i], &cs[(rot_dims >> 1) + i]);
     __syncthreads();
     for (int i = threadIdx.x; i < H * dr; i += blockDim.x) {     // all heads' rotated parts at once
         const int h = i / dr, j = i - h * dr;

@@ -42,16 +42,13 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
     const int t = blockIdx.x;
     const int half = dims >> 1;
     const double pos = (double)positions[t];
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
-        double sn, c;
-        sincos(pos * freq[i], &sn, &c);
-        cs[i] = (float)c;
-        cs[half + i] = (float)sn;
-    }
+    for (int i = threadIdx.x; i < half; i += blockDim.x) rotary_cos_sin(pos, freq[i], &cs[i], &cs[half + i]);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
     float* buf = sm + dims + warp * d;
     float* qall = sm + dims + nwarp * d;             // [H * d], only with qa
+    float* tk = qall + H * d;                        // [H * H], only with qa and talk
+    if (qa && talk) for (int i = threadIdx.x; i < H * H; i += blockDim.x) tk[i] = talk[i];
     const A* row = qkv + (size_t)t * ld;
     const int slot = slots ? slots[t] : -1;
     const int rowlen = G * (d + dv);
@@ -86,18 +83,22 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
     if (!qa) return;
     // the queries of the tensor-core form: [0 (G dv) | for every key/value head c: scale sum_{g in c} M[h, g] q_g]
     __syncthreads();
-    const int hpg = H / G, Dq = G * (d + dv);
+    const int hpg = H / G, Gd = G * d, Gdv = G * dv, Dq = Gd + Gdv;
     A* qrow = qa + (size_t)t * H * Dq;
-    for (int e = threadIdx.x; e < H * Dq; e += blockDim.x) {
-        const int h = e / Dq, j = e - h * Dq;
-        float v = 0.f;
-        if (j >= G * dv) {
-            const int c = (j - G * dv) / d, i = (j - G * dv) - c * d;
-            if (talk) { for (int g = c * hpg; g < (c + 1) * hpg; ++g) v += talk[h * H + g] * qall[g * d + i]; }
+    for (int e = threadIdx.x; e < H * Gdv; e += blockDim.x) {
+        const int h = e / Gdv;
+        qrow[(size_t)h * Dq + (e - h * Gdv)] = from_f32<A>(0.f);
+    }
+    for (int h = 0; h < H; ++h) {
+        const float* trow = tk + h * H;                      // M[h, :] in shared memory
+        A* dst = qrow + (size_t)h * Dq + Gdv;
+        for (int j = threadIdx.x; j < Gd; j += blockDim.x) {
+            const int c = j / d, i = j - c * d;
+            float v = 0.f;
+            if (talk) { for (int g = c * hpg; g < (c + 1) * hpg; ++g) v += trow[g] * qall[g * d + i]; }
             else if (h / hpg == c) v = qall[h * d + i];
-            v *= scale;
+            dst[j] = from_f32<A>(v * scale);
         }
-        qrow[e] = from_f32<A>(v);
     }
 }
 
@@ -108,7 +109,7 @@ extern "C" int rg_talking_prepare(const void* qkv, int dtype, int ld, void* q_ou
     if (T <= 0) return 0;
     if (dims < 0 || dims > d || (dims & 1) || H < 1 || G < 1 || H % G || d < 1 || dv < 1 || (!q_out && !qa))
         return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d + (qa ? H * d : 0)) * sizeof(float);
+    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d + (qa ? H * d + H * H : 0)) * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RG_DTYPE_BF16)

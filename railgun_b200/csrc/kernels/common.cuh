@@ -61,6 +61,16 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// cos and sin of pos * freq for rotary angles.  The product and its reduction to [-pi, pi] are 64-bit (three
+// operations: the angle of a far position keeps all its digits), the functions themselves 32-bit on the small
+// remainder, where they are good to a few 1e-8.
+__device__ __forceinline__ void rotary_cos_sin(double pos, double freq, float* c, float* s) {
+    const double a = pos * freq;
+    const double n = rint(a * 0.15915494309189535);                  // a / (2 pi)
+    const double r = fma(-n, 2.4492935982947064e-16, fma(-n, 6.283185307179586, a));
+    sincosf((float)r, s, c);
+}
+
 #define RG_LAUNCH_RESULT() ((int)cudaGetLastError())
 
 // Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel before it

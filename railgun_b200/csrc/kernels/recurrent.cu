@@ -107,6 +107,133 @@ __global__ void recurrent_scan_kernel(const A* __restrict__ proj, int ld, int y_
         if (j < K - 1) st[(size_t)j * C + c] = tail[j];
 }
 
+// For portions of several tokens the transcendental work leaves the sequential loop: recurrent_gate computes,
+// for every token and channel at once, a = exp(-c r softplus(lam)) and b = sqrt(1 - a^2) i u (the same
+// expressions as above); what is left is S = a S + b along the tokens.
+__global__ void recurrent_gate_kernel(const float* __restrict__ u, const float* __restrict__ gates,
+                                      const float* __restrict__ rb, const float* __restrict__ ib,
+                                      const float* __restrict__ lam, float decay, float* __restrict__ a_out,
+                                      float* __restrict__ b_out, int T, int C, int bs) {
+    const int t = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float sp = decay * rec_softplus(lam[c]);
+    const float brc = rb[c], bic = ib[c];
+    pdl_wait();
+    pdl_trigger();
+    const int blk = c / bs, o = c - blk * bs;
+    const float* g = gates + ((size_t)blk * T + t) * 2 * bs + o;
+    const float log_a = -sp * rec_sigmoid(g[0] + brc);
+    a_out[(size_t)t * C + c] = expf(log_a);
+    b_out[(size_t)t * C + c] = sqrtf(-expm1f(2.f * log_a)) * rec_sigmoid(g[bs] + bic) * u[(size_t)t * C + c];
+}
+
+#define REC_AHEAD 8
+#define REC_CHUNK 64
+// The recurrence is associative, so a request's tokens are cut into chunks of REC_CHUNK that run side by side.
+// recurrent_chunk: within each chunk, from S = 0: a[t] <- the product of the chunk's a up to t, b[t] <- the
+// chunk's own S_t (both in place).  recurrent_finish: the state that enters chunk k is folded from the ends of
+// the chunks before it (S <- b_end + a_end S, starting from the request's stored state), then
+// S_t = b[t] + a[t] S_in, times the gate branch; the request's last chunk leaves S and the convolution's tail
+// in the state slot.  Grid of both: (chunks of the longest request, requests, channels / threads).
+__global__ void recurrent_chunk_kernel(float* __restrict__ a, float* __restrict__ b, const int* __restrict__ cu_seqlens,
+                                       int C) {
+    const int r = blockIdx.y;
+    const int c = blockIdx.z * blockDim.x + threadIdx.x;
+    pdl_wait();
+    pdl_trigger();
+    if (c >= C) return;
+    const int end = cu_seqlens[r + 1];
+    const int lo = cu_seqlens[r] + (int)blockIdx.x * REC_CHUNK, hi = min(end, lo + REC_CHUNK);
+    float P = 1.f, S = 0.f;
+    for (int t0 = lo; t0 < hi; t0 += REC_AHEAD) {
+        float av[REC_AHEAD], bv[REC_AHEAD];
+#pragma unroll
+        for (int k = 0; k < REC_AHEAD; ++k) {
+            const int t = min(t0 + k, hi - 1);
+            av[k] = a[(size_t)t * C + c];
+            bv[k] = b[(size_t)t * C + c];
+        }
+#pragma unroll
+        for (int k = 0; k < REC_AHEAD; ++k) {
+            if (t0 + k < hi) {
+                P *= av[k];
+                S = av[k] * S + bv[k];
+                a[(size_t)(t0 + k) * C + c] = P;
+                b[(size_t)(t0 + k) * C + c] = S;
+            }
+        }
+    }
+}
+
+template <typename A>
+__global__ void recurrent_finish_kernel(const A* __restrict__ proj, int ld, int y_off, int x_off,
+                                        const float* __restrict__ yb, const float* __restrict__ xb,
+                                        const float* __restrict__ a_in, const float* __restrict__ b_in,
+                                        float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                                        const int* __restrict__ start_pos, const int* __restrict__ slots,
+                                        A* __restrict__ out, int out_ld, float out_scale, int C, int K) {
+    const int r = blockIdx.y;
+    const int c = blockIdx.z * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const float byc = yb[c], bxc = xb[c];
+    pdl_wait();
+    pdl_trigger();
+    const int first = cu_seqlens[r], end = cu_seqlens[r + 1];
+    const int lo = first + (int)blockIdx.x * REC_CHUNK, hi = min(end, lo + REC_CHUNK);
+    if (lo >= end) return;
+    const int slot = slots[r];
+    const bool has_past = slot >= 0 && start_pos[r] > 0;
+    float* st = slot >= 0 ? state + (size_t)slot * K * C : nullptr;
+    float S_in = has_past ? st[(size_t)(K - 1) * C + c] : 0.f;
+    for (int j0 = 0; j0 < (int)blockIdx.x; j0 += REC_AHEAD) {        // the ends of the chunks before this one
+        float av[REC_AHEAD], bv[REC_AHEAD];
+#pragma unroll
+        for (int k = 0; k < REC_AHEAD; ++k) {
+            const int j = min(j0 + k, (int)blockIdx.x - 1);
+            const size_t e = (size_t)(first + (j + 1) * REC_CHUNK - 1) * C + c;
+            av[k] = a_in[e];
+            bv[k] = b_in[e];
+        }
+#pragma unroll
+        for (int k = 0; k < REC_AHEAD; ++k)
+            if (j0 + k < (int)blockIdx.x) S_in = bv[k] + av[k] * S_in;
+    }
+    float S = S_in;
+    for (int t0 = lo; t0 < hi; t0 += REC_AHEAD) {
+        float av[REC_AHEAD], bv[REC_AHEAD], gv[REC_AHEAD];
+#pragma unroll
+        for (int k = 0; k < REC_AHEAD; ++k) {
+            const int t = min(t0 + k, hi - 1);
+            av[k] = a_in[(size_t)t * C + c];
+            bv[k] = b_in[(size_t)t * C + c];
+            gv[k] = to_f32(proj[(size_t)t * ld + y_off + c]);
+        }
+#pragma unroll
+        for (int k = 0; k < REC_AHEAD; ++k) {
+            if (t0 + k < hi) {
+                S = bv[k] + av[k] * S_in;
+                out[(size_t)(t0 + k) * out_ld + c] = from_f32<A>(S * rec_gelu_tanh(gv[k] + byc) * out_scale);
+            }
+        }
+    }
+    if (!st || hi != end) return;
+    st[(size_t)(K - 1) * C + c] = S;
+    const int n = end - first;
+    float tail[REC_MAX_TAPS];
+#pragma unroll
+    for (int j = 0; j < REC_MAX_TAPS; ++j) {
+        if (j < K - 1) {
+            const int src = n - (K - 1) + j;
+            if (src >= 0) tail[j] = to_f32(proj[(size_t)(first + src) * ld + x_off + c]) + bxc;
+            else tail[j] = has_past ? st[(size_t)(n + j) * C + c] : 0.f;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < REC_MAX_TAPS; ++j)
+        if (j < K - 1) st[(size_t)j * C + c] = tail[j];
+}
+
 extern "C" int rg_recurrent_conv(const void* proj, int dtype, int ld, int x_off, const float* xb, const float* taps,
                                  const float* cb, const float* state, const int* cu_seqlens, const int* req_of_token,
                                  const int* start_pos, const int* slots, float* u, int T, int C, int K, void* stream) {
@@ -127,11 +254,33 @@ extern "C" int rg_recurrent_scan(const void* proj, int dtype, int ld, int y_off,
                                  const float* xb, const float* u, const float* gates, const float* rb, const float* ib,
                                  const float* lam, float decay, float* state, const int* cu_seqlens,
                                  const int* start_pos, const int* slots, void* out, int out_ld, float out_scale, int T,
-                                 int R, int C, int K, int bs, void* stream) {
+                                 int R, int C, int K, int bs, float* ab, int max_tokens, void* stream) {
     if (T <= 0 || R <= 0) return 0;
     if (C < 1 || K < 1 || K > REC_MAX_TAPS || bs < 1 || C % bs) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(R, (C + REC_THREADS - 1) / REC_THREADS);
+    if (ab) {
+        // portions of several tokens: the gates of all tokens at once (ab: room for 2 T C floats), then the
+        // recurrence in chunks side by side
+        float* a_buf = ab;
+        float* b_buf = ab + (size_t)T * C;
+        if (max_tokens < 1 || R > 65535 || grid.y > 65535) return RG_ERR_UNSUPPORTED;
+        int e = rg_launch(recurrent_gate_kernel, dim3(T, grid.y), dim3(REC_THREADS), 0, s, 1, u, gates, rb, ib, lam, decay,
+                          a_buf, b_buf, T, C, bs);
+        if (e) return e;
+        dim3 cgrid((max_tokens + REC_CHUNK - 1) / REC_CHUNK, R, grid.y);
+        e = rg_launch(recurrent_chunk_kernel, cgrid, dim3(REC_THREADS), 0, s, 1, a_buf, b_buf, cu_seqlens, C);
+        if (e) return e;
+        if (dtype == RG_DTYPE_BF16)
+            return rg_launch(recurrent_finish_kernel<bf16>, cgrid, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, y_off,
+                             x_off, yb, xb, (const float*)a_buf, (const float*)b_buf, state, cu_seqlens, start_pos, slots,
+                             (bf16*)out, out_ld, out_scale, C, K);
+        if (dtype == RG_DTYPE_F32)
+            return rg_launch(recurrent_finish_kernel<float>, cgrid, dim3(REC_THREADS), 0, s, 1, (const float*)proj, ld,
+                             y_off, x_off, yb, xb, (const float*)a_buf, (const float*)b_buf, state, cu_seqlens, start_pos,
+                             slots, (float*)out, out_ld, out_scale, C, K);
+        return RG_ERR_UNSUPPORTED;
+    }
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(recurrent_scan_kernel<bf16>, grid, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, y_off,
                          x_off, yb, xb, u, gates, rb, ib, lam, decay, state, cu_seqlens, start_pos, slots, (bf16*)out,

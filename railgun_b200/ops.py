@@ -633,6 +633,10 @@ def recurrent_conv(proj: torch.Tensor, x_off: int, xb: torch.Tensor, taps: torch
     return u
 
 
+# Steps whose longest portion is at most this many tokens compute gates and recurrence in one kernel.
+RECURRENT_FUSED_MAX_TOKENS = 4
+
+
 def recurrent_scan(proj: torch.Tensor, y_off: int, x_off: int, yb, xb, u: torch.Tensor, gates: torch.Tensor, rb, ib, lam,
                    decay: float, state: torch.Tensor, batch, out: torch.Tensor | None = None,
                    out_scale: float = 1.0) -> torch.Tensor:
@@ -654,11 +658,16 @@ def recurrent_scan(proj: torch.Tensor, y_off: int, x_off: int, yb, xb, u: torch.
         out = torch.empty((T, C), dtype=proj.dtype, device=proj.device)
     _check_out_view(out, T, C, proj.dtype, "recurrent_scan")
     R = batch.cu_seqlens.numel() - 1
+    # portions of several tokens: the gates of all tokens in one parallel kernel, then the bare recurrence
+    ab = None
+    if batch.max_query_len > RECURRENT_FUSED_MAX_TOKENS:
+        ab = torch.empty((2, T, C), dtype=torch.float32, device=proj.device)
+        _COUNTER.value += 2
     _ok(_fn("recurrent", "rg_recurrent_scan")(
         _ptr(proj), c_int(_dtype_code(proj)), c_int(proj.stride(0)), c_int(y_off), c_int(x_off), _ptr(yb), _ptr(xb),
         _ptr(u), _ptr(gates), _ptr(rb), _ptr(ib), _ptr(lam), c_float(decay), _ptr(state), _ptr(batch.cu_seqlens),
         _ptr(batch.start_pos), _ptr(batch.state_slots), _ptr(out), c_int(out.stride(0)), c_float(out_scale), c_int(T),
-        c_int(R), c_int(C), c_int(K), c_int(bs), _stream()), "recurrent_scan")
+        c_int(R), c_int(C), c_int(K), c_int(bs), _ptr(ab), c_int(batch.max_query_len), _stream()), "recurrent_scan")
     return out
 
 
