@@ -309,10 +309,14 @@ def latent_attention_general(qa: torch.Tensor, cache: torch.Tensor, block_table:
     return out
 
 
+# RAILGUN_B200_LATENT_MMA=0 sends everything that would run the tensor-core latent-cache kernel to the general one.
+USE_LATENT_MMA = os.environ.get("RAILGUN_B200_LATENT_MMA", "1") != "0"
+
+
 def latent_attention_mma_ok(dtype, H: int, R: int, D: int) -> bool:
     """Whether the tensor-core kernels take these sizes: bfloat16, latent and row sizes in steps of 16, a latent
     of at most 512 numbers, a row that fits shared memory."""
-    if dtype != torch.bfloat16 or R % 16 or D % 16 or not 16 <= R <= 512 or D < R:
+    if not USE_LATENT_MMA or dtype != torch.bfloat16 or R % 16 or D % 16 or not 16 <= R <= 512 or D < R:
         return False
     return (64 + 64) * (D + 8) * 2 + 4 * 16 * 40 * 2 + 4 * 128 * 4 <= 227 * 1024
 
