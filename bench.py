@@ -817,6 +817,105 @@ def run_kernels(args):
                 llama_tcgen05_us=round(us2, 2), llama_tcgen05_TFLOPs=round(fl2 / us2 / 1e6, 1),
                 llama_tcgen05_frac=round(fl2 / us2 / 1e6 / pk["bf16_tflops"], 3),
                 llama_mma_sync_us=round(us3, 2), llama_mma_sync_TFLOPs=round(fl2 / us3 / 1e6, 1))
+    if on("talking_attention"):
+        # talking-heads attention (heads x key/value heads x key size = value size) on the tensor cores beside the
+        # dense model's kernels at equal width: single tokens by bytes of cache read, prompts by the design's own
+        # FLOPs (scores and values once per head and key, and the mixing of the heads' scores)
+        from types import SimpleNamespace
+        pk, _ = peaks()
+        for Hh, G, dd in ((16, 2, 128), (8, 2, 64)):
+            R, D, hpg = G * dd, 2 * G * dd, Hh // G
+            for B, ctx in ((8, 1024), (64, 1024)):
+                blocks = -(-ctx // page)
+                caches = [torch.randn(B * blocks, page, D, device=dev).to(torch.bfloat16) for _ in range(L)]
+                bt = torch.arange(B * blocks, dtype=torch.int32, device=dev).view(B, blocks).contiguous()
+                qa = torch.randn(B, Hh, D, device=dev).to(torch.bfloat16)
+                o = torch.empty(B, Hh * dd, dtype=torch.bfloat16, device=dev)
+                req = torch.arange(B, dtype=torch.int32, device=dev)
+                pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+                sp = ops.latent_decode_splits(B, 1, ctx)
+                us = timed(lambda: [ops.latent_attention_mma(qa, o, c, bt, None, None, B, req, pos, R, 0, 1.0, sp,
+                                                             select=(dd, hpg), score_from=R) for c in caches])
+                kvs = [torch.randn(B * blocks, 2, nkv, page, d, device=dev).to(torch.bfloat16) for _ in range(L)]
+                q = torch.randn(B, QKV, device=dev).to(torch.bfloat16)
+                o2 = torch.empty(B, nh * d, dtype=torch.bfloat16, device=dev)
+                sp2 = ops.decode_splits(B, nkv, ctx)
+                us2 = timed(lambda: [ops.decode_attention(q, QKV, o2, kv, bt, None, B, req, pos, nh, nkv, d, 0, d ** -0.5, sp2) for kv in kvs])
+                gbs, gbs2 = B * ctx * D * 2 / us / 1e3, B * ctx * nkv * d * 4 / us2 / 1e3
+                out(f"talking decode attention H{Hh} G{G} d{dd} B{B} ctx{ctx}", us, GBs=round(gbs, 1),
+                    frac=round(gbs / pk["hbm_gbs"], 3), llama_us=round(us2, 2), llama_GBs=round(gbs2, 1),
+                    llama_frac=round(gbs2 / pk["hbm_gbs"], 3))
+            T = 2048
+            blocks = -(-T // page)
+            caches = [torch.randn(blocks, page, D, device=dev).to(torch.bfloat16) for _ in range(L)]
+            bt = torch.arange(blocks, dtype=torch.int32, device=dev).view(1, blocks).contiguous()
+            qa = torch.randn(T, Hh, D, device=dev).to(torch.bfloat16)
+            qc = torch.randn(T, Hh, G * dd, device=dev).to(torch.bfloat16)
+            o = torch.empty(T, Hh * dd, dtype=torch.bfloat16, device=dev)
+            pos = torch.arange(T, dtype=torch.int32, device=dev)
+            req = torch.zeros(T, dtype=torch.int32, device=dev)
+            t64 = torch.tensor([(k, min(64, T - k), 0) for k in range(0, T, 64)], dtype=torch.int32, device=dev)
+            us_rows = timed(lambda: [ops.latent_attention_mma(qa, o, c, bt, t64, None, t64.shape[0], req, pos, R, 0, 1.0,
+                                                              select=(dd, hpg), score_from=R) for c in caches])
+            batch = SimpleNamespace(cu_seqlens=torch.tensor([0, T], dtype=torch.int32, device=dev),
+                                    context_lens=torch.tensor([T], dtype=torch.int32, device=dev), prefill_tiles=t64,
+                                    positions=pos, req_of_token=req)
+            ops.TALKING_FLASH_MAX_KEYS, kept = 256, ops.TALKING_FLASH_MAX_KEYS        # time both forms at every size
+            us_flash = timed(lambda: [ops.talking_prefill_flash(qc, c, bt, batch, G, dd, dd, o) for c in caches])
+            ops.TALKING_FLASH_MAX_KEYS = kept
+            fl = (Hh * 4 * dd + 2 * Hh * Hh) * T * (T + 1) / 2
+            kvs = [torch.randn(blocks, 2, nkv, page, d, device=dev).to(torch.bfloat16) for _ in range(L)]
+            q = torch.randn(T, QKV, device=dev).to(torch.bfloat16)
+            o2 = torch.empty(T, nh * d, dtype=torch.bfloat16, device=dev)
+            t128 = torch.tensor([(k, min(128, T - k), 0) for k in range(0, T, 128)], dtype=torch.int32, device=dev)
+            fl2 = nh * 4 * d * T * (T + 1) / 2
+            us2 = timed(lambda: [ops.prefill_attention_tc(q, o2, kv, bt, t128, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
+            us3 = timed(lambda: [ops.prefill_attention(q, QKV, o2, kv, bt, t64, pos, nh, nkv, d, 0, d ** -0.5) for kv in kvs])
+            out(f"talking prompt attention H{Hh} G{G} d{dd} T{T}", min(us_rows, us_flash), rows_form_us=round(us_rows, 2),
+                flash_form_us=round(us_flash, 2), TFLOPs=round(fl / min(us_rows, us_flash) / 1e6, 1),
+                frac=round(fl / min(us_rows, us_flash) / 1e6 / pk["bf16_tflops"], 3),
+                llama_tcgen05_us=round(us2, 2), llama_tcgen05_frac=round(fl2 / us2 / 1e6 / pk["bf16_tflops"], 3),
+                llama_mma_sync_us=round(us3, 2), llama_mma_sync_frac=round(fl2 / us3 / 1e6 / pk["bf16_tflops"], 3))
+    if on("rupulix_rows"):
+        # the memory kernels of the hyper-connected stream and of the recurrence, by bytes they have to move, beside
+        # the dense model's residual-add + RMSNorm kernel
+        from types import SimpleNamespace
+        pk, _ = peaks()
+        W, S, C, K, Bk = 2048, 2, 2048, 4, 8
+        for T in (8, 2048):
+            cps = [torch.randn(T, S, W, device=dev) for _ in range(L)]
+            ys = [torch.randn(T, W, device=dev).to(torch.bfloat16) for _ in range(L)]
+            mix, oc, ic, nw = torch.eye(S, device=dev), torch.ones(S, device=dev), torch.ones(S, device=dev), torch.ones(W, device=dev)
+            us = timed(lambda: [ops.hyper_step(c, None, y, mix, oc, ic, nw, 1e-6, torch.bfloat16) for c, y in zip(cps, ys)])
+            by = T * W * (8 * S + 2 + 2)
+            rs = [torch.randn(T, W, device=dev) for _ in range(L)]
+            us2 = timed(lambda: [ops.add_rmsnorm(r, y, nw, 1e-6, torch.bfloat16) for r, y in zip(rs, ys)])
+            by2 = T * W * (8 + 2 + 2)
+            out(f"hyper step S{S} W{W} T{T}", us, GBs=round(by / us / 1e3, 1), frac=round(by / us / 1e3 / pk["hbm_gbs"], 3),
+                add_rmsnorm_us=round(us2, 2), add_rmsnorm_frac=round(by2 / us2 / 1e3 / pk["hbm_gbs"], 3))
+            R_ = 1 if T > 8 else T
+            per = T // R_
+            batch = SimpleNamespace(cu_seqlens=torch.arange(0, T + 1, per, dtype=torch.int32, device=dev),
+                                    req_of_token=(torch.arange(T, device=dev) // per).to(torch.int32),
+                                    start_pos=torch.zeros(R_, dtype=torch.int32, device=dev),
+                                    state_slots=torch.arange(R_, dtype=torch.int32, device=dev), max_query_len=per)
+            projs = [torch.randn(T, 2 * C, device=dev).to(torch.bfloat16) for _ in range(L)]
+            vec = lambda n: torch.randn(n, device=dev) * 0.1
+            xb, yb, cb, rb, ib, lam = vec(C), vec(C), vec(C), vec(C), vec(C), vec(C) - 3.0
+            taps = torch.randn(C, K, device=dev) * 0.3
+            state = torch.zeros(R_, K, C, device=dev)
+            wg = torch.randn(Bk, C // Bk, 2 * C // Bk, device=dev) * 0.05
+            us_c = timed(lambda: [ops.recurrent_conv(p, C, xb, taps, cb, state, batch) for p in projs])
+            us_ = [ops.recurrent_conv(p, C, xb, taps, cb, state, batch) for p in projs]
+            us_g = timed(lambda: [torch.bmm(u.view(-1, Bk, C // Bk).transpose(0, 1), wg) for u in us_])
+            gs = [torch.bmm(u.view(-1, Bk, C // Bk).transpose(0, 1), wg) for u in us_]
+            us_s = timed(lambda: [ops.recurrent_scan(p, 0, C, yb, xb, u, g, rb, ib, lam, 8.0, state, batch)
+                                  for p, u, g in zip(projs, us_, gs)])
+            by_c, by_s = T * C * (2 + 4), T * C * (4 + 8 + 2 + 2)
+            out(f"recurrence C{C} blocks{Bk} taps{K} T{T}", us_c + us_g + us_s, conv_us=round(us_c, 2),
+                conv_frac=round(by_c / us_c / 1e3 / pk["hbm_gbs"], 3), gates_product_us=round(us_g, 2),
+                gates_TFLOPs=round(2 * T * C * 2 * (C // Bk) / us_g / 1e6, 2), scan_us=round(us_s, 2),
+                scan_frac=round(by_s / us_s / 1e3 / pk["hbm_gbs"], 3))
     if on("moe"):
         # the routed experts' two grouped products (32 experts of 1,024 at width 2,048, 4 choices) beside the dense
         # model's gate|up and down products of equal work: decode by bytes of weights read, prompts by FLOP/s

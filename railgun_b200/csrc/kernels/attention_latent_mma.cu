@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
         const int* __restrict__ tiles, int sub, int tt, const int* __restrict__ rows_list,
         const int* __restrict__ req_of_token, const int* __restrict__ positions, int H, int hc, int R, int D,
         int page_size, int window, float scale_log2, int nsplit, const float* __restrict__ sink, int sel_dv, int sel_hpg,
-        int out_ld, float out_scale) {
+        int out_ld, float out_scale, int kd0) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int GT = 32 * CW;                                    // threads of a row group
     constexpr int KW = LM_BN / CW;                                 // keys a warp scores per tile: 16 or 8
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(
             const bf16* krow = CW == 2 ? sKs + (cw * KW + b_key) * stride + b_dim
                                        : sKs + (cw * KW + (lane & 7)) * stride + ((lane >> 3) & 1) * 8;
 #pragma unroll 1
-            for (int kd = 0; kd < d16; kd += NCH) {
+            for (int kd = kd0; kd < d16; kd += NCH) {           // kd0 > 0: the queries' first 16 kd0 numbers are zeros
                 uint32_t a[NCH][4], b[NCH][4];
 #pragma unroll
                 for (int c = 0; c < NCH; ++c) {
@@ -350,7 +350,8 @@ __global__ void latent_merge_kernel(const float* __restrict__ part_o, const floa
 // Options of both kernels: `sink` [H] (exp(sink[h]) joins head h's denominator once: in the kernel without
 // shares, in the merge with them); `sel_dv` > 0: head h keeps only columns [(h / sel_hpg) sel_dv, + sel_dv) of
 // its R output numbers and writes them to out[token * out_ld + h * sel_dv + c] (a cache row that holds several
-// value heads side by side, of which a head wants its own); `out_scale` multiplies the result.
+// value heads side by side, of which a head wants its own); `out_scale` multiplies the result; `score_from`
+// (a multiple of 16): the scores run over the row's numbers from there on only (the queries are zero before).
 template <typename K> static int lm_allow_smem(K kernel, size_t bytes) {
     return (int)cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
@@ -374,8 +375,9 @@ extern "C" int rg_latent_attention_mma(
         const void* qa, void* out, float* part_o, float* part_ml, const void* cache, const int* block_table,
         int max_blocks, const int* tiles, const int* rows_list, int n_items, const int* req_of_token,
         const int* positions, int H, int R, int D, int page_size, int window, float scale, int nsplit,
-        const float* sink, int sel_dv, int sel_hpg, int out_ld, float out_scale, void* stream) {
+        const float* sink, int sel_dv, int sel_hpg, int out_ld, float out_scale, int score_from, void* stream) {
     if (n_items <= 0) return 0;
+    if (score_from < 0 || score_from % 16 || score_from >= D) return RG_ERR_UNSUPPORTED;
     if (sel_dv < 0 || (sel_dv > 0 && (sel_hpg < 1 || (sel_dv & 1) || ((H + sel_hpg - 1) / sel_hpg) * sel_dv > R)))
         return RG_ERR_UNSUPPORTED;
     if (rg_latent_attention_mma_ok(H, R, D) || page_size < 1 || nsplit < 1 || nsplit > 65535) return RG_ERR_UNSUPPORTED;
@@ -400,7 +402,7 @@ extern "C" int rg_latent_attention_mma(
 #define RG_LM(N, C) { e = lm_allow_smem(latent_attention_mma_kernel<N, C>, smem); if (e) return e; \
         e = rg_launch(latent_attention_mma_kernel<N, C>, grid, block, smem, s, 1, (const bf16*)qa, (bf16*)out, part_o, part_ml, \
                       (const bf16*)cache, block_table, max_blocks, tiles, sub, tt, rows_list, req_of_token, positions, H, hc, \
-                      R, D, page_size, window, scale_log2, nsplit, sink, sel_dv, sel_hpg, out_ld, out_scale); }
+                      R, D, page_size, window, scale_log2, nsplit, sink, sel_dv, sel_hpg, out_ld, out_scale, score_from >> 4); }
     if (CW == 2) { if (ndh <= 8) RG_LM(8, 2) else if (ndh <= 16) RG_LM(16, 2) else RG_LM(32, 2) }
     else { if (ndh <= 4) RG_LM(4, 4) else if (ndh <= 8) RG_LM(8, 4) else RG_LM(16, 4) }
 #undef RG_LM

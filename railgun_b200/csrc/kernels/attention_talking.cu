@@ -21,7 +21,8 @@
 // the mixed score is s'_h[i, j] = Q'_h[i] . K_j: every head attends to the same rows, as in attention over a
 // latent cache, and that kernel (attention_latent_mma.cu) runs it: its queries are [0 (G dv) | Q'_h], its
 // scores run over the whole cache row [V | K], its values are the row's first G dv numbers, of which head h
-// keeps the dv of its own key/value head.  talking_prepare writes those queries when asked (qa).
+// keeps the dv of its own key/value head.  talking_prepare writes those queries when asked (qa).  Prompts can
+// also run on the flash kernel of ordinary paged attention (talking_pack_kv, talking_select below).
 #include "common.cuh"
 
 #define TK_THREADS 128
@@ -34,7 +35,8 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                                        const double* __restrict__ freq, int dims, const int* __restrict__ positions,
                                        const int* __restrict__ slots, int H, int G, int d, int dv,
-                                       A* __restrict__ qa, const float* __restrict__ talk, float scale) {
+                                       A* __restrict__ qa, const float* __restrict__ talk, float scale,
+                                       A* __restrict__ qc) {
     extern __shared__ float sm[];                    // cos | sin of the token's dims / 2 angles, then one head's numbers per warp
     float* cs = sm;                                  // (and, for qa, all heads' rotated queries behind them)
     pdl_wait();
@@ -48,7 +50,8 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
     float* buf = sm + dims + warp * d;
     float* qall = sm + dims + nwarp * d;             // [H * d], only with qa
     float* tk = qall + H * d;                        // [H * H], only with qa and talk
-    if (qa && talk) for (int i = threadIdx.x; i < H * H; i += blockDim.x) tk[i] = talk[i];
+    const bool mixes = qa || qc;
+    if (mixes && talk) for (int i = threadIdx.x; i < H * H; i += blockDim.x) tk[i] = talk[i];
     const A* row = qkv + (size_t)t * ld;
     const int slot = slots ? slots[t] : -1;
     const int rowlen = G * (d + dv);
@@ -71,7 +74,7 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
             if (i < half) v = v * cs[i] - buf[i + half] * inv * (w ? w[i + half] : 1.f) * cs[half + i];
             else if (i < dims) v = v * cs[i - half] + buf[i - half] * inv * (w ? w[i - half] : 1.f) * cs[i];
             if (dst) dst[i] = from_f32<A>(v);
-            if (is_q && qa) qall[hh * d + i] = v;
+            if (is_q && mixes) qall[hh * d + i] = v;
         }
         __syncwarp();
     }
@@ -80,46 +83,125 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
         A* vdst = cache + (size_t)slot * rowlen;
         for (int i = threadIdx.x; i < G * dv; i += blockDim.x) vdst[i] = vsrc[i];
     }
-    if (!qa) return;
-    // the queries of the tensor-core form: [0 (G dv) | for every key/value head c: scale sum_{g in c} M[h, g] q_g]
+    if (!mixes) return;
+    // the queries of the tensor-core forms: for every key/value head c the numbers scale sum_{g in c} M[h, g] q_g,
+    // behind G dv zeros in qa [T, H, G dv + G d] and on their own in qc [T, H, G d]
     __syncthreads();
     const int hpg = H / G, Gd = G * d, Gdv = G * dv, Dq = Gd + Gdv;
-    A* qrow = qa + (size_t)t * H * Dq;
-    for (int e = threadIdx.x; e < H * Gdv; e += blockDim.x) {
-        const int h = e / Gdv;
-        qrow[(size_t)h * Dq + (e - h * Gdv)] = from_f32<A>(0.f);
+    if (qa) {
+        A* qrow = qa + (size_t)t * H * Dq;
+        for (int e = threadIdx.x; e < H * Gdv; e += blockDim.x) {
+            const int h = e / Gdv;
+            qrow[(size_t)h * Dq + (e - h * Gdv)] = from_f32<A>(0.f);
+        }
     }
     for (int h = 0; h < H; ++h) {
         const float* trow = tk + h * H;                      // M[h, :] in shared memory
-        A* dst = qrow + (size_t)h * Dq + Gdv;
         for (int j = threadIdx.x; j < Gd; j += blockDim.x) {
             const int c = j / d, i = j - c * d;
             float v = 0.f;
             if (talk) { for (int g = c * hpg; g < (c + 1) * hpg; ++g) v += trow[g] * qall[g * d + i]; }
             else if (h / hpg == c) v = qall[h * d + i];
-            dst[j] = from_f32<A>(v * scale);
+            if (qa) qa[((size_t)t * H + h) * Dq + Gdv + j] = from_f32<A>(v * scale);
+            if (qc) qc[((size_t)t * H + h) * Gd + j] = from_f32<A>(v * scale);
         }
     }
+}
+
+// Prompts on the flash kernel of ordinary paged attention.  With the queries mixed (qc above) a head's score is
+// Q'_h . [k_0 | ... | k_(G-1)]: the contexts of the step's requests that bring several tokens are laid out as
+// temporary key/value pages [requests * max_blocks, 2, G, page_size, G d] in which every key/value head c has the
+// same keys, all G key heads side by side, and its own values v_c, zero-padded from dv to G d; page j of the
+// step's request r is page r * max_blocks + j.  talking_select then keeps the first dv numbers of every head's
+// output row, times a constant, for the rows of those requests.
+template <typename A>
+__global__ void talking_pack_kv_kernel(const A* __restrict__ cache, const int* __restrict__ block_table, int max_blocks,
+                                       const int* __restrict__ cu_seqlens, const int* __restrict__ context_lens,
+                                       A* __restrict__ kv, int page_size, int G, int d, int dv) {
+    pdl_wait();
+    pdl_trigger();
+    const int j = blockIdx.x, r = blockIdx.y;
+    if (cu_seqlens[r + 1] - cu_seqlens[r] < 2) return;
+    const int ctx = context_lens[r];
+    if (j * page_size >= ctx) return;
+    const int page = block_table[(size_t)r * max_blocks + j];
+    if (page < 0) return;
+    const int n = min(page_size, ctx - j * page_size);
+    const int Gd = G * d, Gdv = G * dv, rowlen = Gd + Gdv;
+    const A* src = cache + (size_t)page * page_size * rowlen;
+    A* kdst = kv + ((size_t)r * max_blocks + j) * 2 * G * page_size * Gd;
+    A* vdst = kdst + (size_t)G * page_size * Gd;
+    for (int i = threadIdx.x; i < G * n * Gd; i += blockDim.x) {
+        const int c = i / (n * Gd), rem = i - c * n * Gd, o = rem / Gd, col = rem - o * Gd;
+        kdst[((size_t)c * page_size + o) * Gd + col] = src[(size_t)o * rowlen + Gdv + col];
+        vdst[((size_t)c * page_size + o) * Gd + col] = col < dv ? src[(size_t)o * rowlen + c * dv + col] : from_f32<A>(0.f);
+    }
+}
+
+extern "C" int rg_talking_pack_kv(const void* cache, const int* block_table, int max_blocks, const int* cu_seqlens,
+                                  const int* context_lens, void* kv, int dtype, int requests, int page_size, int G, int d,
+                                  int dv, void* stream) {
+    if (requests <= 0 || max_blocks <= 0) return 0;
+    if (dv > G * d || requests > 65535) return RG_ERR_UNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    dim3 grid(max_blocks, requests);
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(talking_pack_kv_kernel<bf16>, grid, dim3(256), 0, s, 1, (const bf16*)cache, block_table, max_blocks,
+                         cu_seqlens, context_lens, (bf16*)kv, page_size, G, d, dv);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(talking_pack_kv_kernel<float>, grid, dim3(256), 0, s, 1, (const float*)cache, block_table,
+                         max_blocks, cu_seqlens, context_lens, (float*)kv, page_size, G, d, dv);
+    return RG_ERR_UNSUPPORTED;
+}
+
+// wide [T, H * Gd] -> out[t, h * dv + c] = wide[t, h * Gd + c] * out_scale, for the rows of requests with several tokens
+template <typename A>
+__global__ void talking_select_kernel(const A* __restrict__ wide, A* __restrict__ out, int out_ld, float out_scale,
+                                      const int* __restrict__ cu_seqlens, const int* __restrict__ req_of_token, int H,
+                                      int Gd, int dv) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int r = req_of_token[t];
+    if (cu_seqlens[r + 1] - cu_seqlens[r] < 2) return;
+    for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
+        const int h = e / dv, c = e - h * dv;
+        out[(size_t)t * out_ld + e] = from_f32<A>(to_f32(wide[((size_t)t * H + h) * Gd + c]) * out_scale);
+    }
+}
+
+extern "C" int rg_talking_select(const void* wide, void* out, int out_ld, float out_scale, int dtype,
+                                 const int* cu_seqlens, const int* req_of_token, int T, int H, int Gd, int dv,
+                                 void* stream) {
+    if (T <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == RG_DTYPE_BF16)
+        return rg_launch(talking_select_kernel<bf16>, dim3(T), dim3(256), 0, s, 1, (const bf16*)wide, (bf16*)out, out_ld,
+                         out_scale, cu_seqlens, req_of_token, H, Gd, dv);
+    if (dtype == RG_DTYPE_F32)
+        return rg_launch(talking_select_kernel<float>, dim3(T), dim3(256), 0, s, 1, (const float*)wide, (float*)out, out_ld,
+                         out_scale, cu_seqlens, req_of_token, H, Gd, dv);
+    return RG_ERR_UNSUPPORTED;
 }
 
 extern "C" int rg_talking_prepare(const void* qkv, int dtype, int ld, void* q_out, void* cache, const float* q_norm,
                                   const float* k_norm, float eps, const double* freq, int dims, const int* positions,
                                   const int* slots, int T, int H, int G, int d, int dv, void* qa, const float* talk,
-                                  float scale, void* stream) {
+                                  float scale, void* qc, void* stream) {
     if (T <= 0) return 0;
-    if (dims < 0 || dims > d || (dims & 1) || H < 1 || G < 1 || H % G || d < 1 || dv < 1 || (!q_out && !qa))
+    if (dims < 0 || dims > d || (dims & 1) || H < 1 || G < 1 || H % G || d < 1 || dv < 1 || (!q_out && !qa && !qc))
         return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d + (qa ? H * d + H * H : 0)) * sizeof(float);
+    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d + ((qa || qc) ? H * d + H * H : 0)) * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(talking_prepare_kernel<bf16>, dim3(T), dim3(TK_THREADS), smem, s, 1, (const bf16*)qkv, ld,
                          (bf16*)q_out, (bf16*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv,
-                         (bf16*)qa, talk, scale);
+                         (bf16*)qa, talk, scale, (bf16*)qc);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(talking_prepare_kernel<float>, dim3(T), dim3(TK_THREADS), smem, s, 1, (const float*)qkv, ld,
                          (float*)q_out, (float*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv,
-                         (float*)qa, talk, scale);
+                         (float*)qa, talk, scale, (float*)qc);
     return RG_ERR_UNSUPPORTED;
 }
 

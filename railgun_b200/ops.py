@@ -332,13 +332,14 @@ def latent_decode_splits(n_tokens: int, head_chunks: int, max_context: int) -> i
 def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tiles,
                          rows, n_items: int, req_of_token: torch.Tensor, positions: torch.Tensor, R: int, window: int,
                          scale: float, num_splits: int = 1, sink: torch.Tensor | None = None, select=None,
-                         out_scale: float = 1.0) -> None:
+                         out_scale: float = 1.0, score_from: int = 0) -> None:
     """Attention over the latent cache on the tensor cores, into ``out`` [T, H, R].  With ``tiles`` [n, 3]
     (first row, rows <= 64, request): requests with several tokens.  Without: ``n_items`` single tokens
     (``rows``, or rows 0..n_items-1), every context cut into ``num_splits`` shares that a second kernel adds.
     ``sink`` [H] float32: exp(sink[h]) joins head h's denominator.  ``select`` = (dv, heads per group): head h
     keeps only columns [(h // heads per group) dv, + dv) of its R output numbers, and ``out`` is a [T, H dv] view
-    (rows may be further apart).  ``out_scale`` multiplies the result."""
+    (rows may be further apart).  ``out_scale`` multiplies the result.  ``score_from`` (a multiple of 16): the
+    scores use the row's numbers from there on only; the queries must be zero before it."""
     _check(qa, "qa", torch.bfloat16)
     _check(cache, "cache", torch.bfloat16)
     _check(block_table, "block_table", torch.int32)
@@ -374,7 +375,8 @@ def latent_attention_mma(qa: torch.Tensor, out: torch.Tensor, cache: torch.Tenso
         _ptr(qa), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(cache), _ptr(block_table), c_int(block_table.shape[1]),
         _ptr(tiles), _ptr(rows), c_int(n_items), _ptr(req_of_token), _ptr(positions), c_int(H), c_int(R), c_int(D),
         c_int(cache.shape[1]), c_int(window or 0), c_float(scale), c_int(num_splits if tiles is None else 1),
-        _ptr(sink), c_int(sel_dv), c_int(sel_hpg), c_int(out_ld), c_float(out_scale), _stream()), "latent_attention_mma")
+        _ptr(sink), c_int(sel_dv), c_int(sel_hpg), c_int(out_ld), c_float(out_scale), c_int(score_from), _stream()),
+        "latent_attention_mma")
 
 
 MOE_TILE_ROWS = 32
@@ -539,15 +541,21 @@ def hyper_step(copies, x0, y, mix, outc, inc, norm_w, eps: float, out_dtype, out
 
 def talking_prepare(qkv: torch.Tensor, q_out, cache, q_norm, k_norm, eps: float, freq: torch.Tensor,
                     rot_dims: int, positions: torch.Tensor, slots, H: int, G: int, d: int, dv: int,
-                    qa: torch.Tensor | None = None, talk=None, scale: float = 1.0) -> None:
+                    qa: torch.Tensor | None = None, talk=None, scale: float = 1.0,
+                    qc: torch.Tensor | None = None) -> None:
     """Per token of ``qkv`` [T, H d + G d + G dv]: every q and k head is RMS-normed over its d numbers
     (``q_norm`` / ``k_norm`` [d] float32, None: no norm) and its first ``rot_dims`` numbers are rotated in
     pairs (i, i + rot_dims / 2) by position * ``freq[i]`` (float64); q goes to ``q_out`` [T, H, d] (if given),
     the values and the keys to row ``slots[t]`` of ``cache`` [pages, page, G dv + G d] (negative slot or None: no
     write).  ``qa`` [T, H, G dv + G d] (if given) receives the queries of the tensor-core form: zeros, then for
-    every key/value head c the numbers ``scale`` * sum over the heads g of c of ``talk``[h, g] q_g."""
+    every key/value head c the numbers ``scale`` * sum over the heads g of c of ``talk``[h, g] q_g; ``qc``
+    [T, H, G d] (if given) the same without the zeros."""
     _check(qkv, "qkv")
-    if q_out is None and qa is None:
+    if qc is not None:
+        _check(qc, "qc", qkv.dtype)
+        if qc.shape != (qkv.shape[0], H, G * d):
+            raise KernelError(f"talking_prepare: qc {tuple(qc.shape)} is not [T, {H}, {G * d}]")
+    if q_out is None and qa is None and qc is None:
         raise KernelError("talking_prepare: nowhere to put the queries")
     _check(freq, "freq", torch.float64)
     _check(positions, "positions", torch.int32)
@@ -558,8 +566,8 @@ def talking_prepare(qkv: torch.Tensor, q_out, cache, q_norm, k_norm, eps: float,
         _check(qa, "qa", qkv.dtype)
         if qa.shape != (T, H, G * (d + dv)):
             raise KernelError(f"talking_prepare: qa {tuple(qa.shape)} is not [T, {H}, {G * (d + dv)}]")
-        if talk is not None:
-            _check(talk, "talk", torch.float32)
+    if talk is not None:
+        _check(talk, "talk", torch.float32)
     if (qkv.shape[1] != (H + G) * d + G * dv or (q_out is not None and q_out.shape != (T, H, d))
             or positions.numel() != T):
         raise KernelError(f"talking_prepare: qkv {tuple(qkv.shape)} does not match {H} + {G} heads of {d}, values of {dv}")
@@ -580,7 +588,45 @@ def talking_prepare(qkv: torch.Tensor, q_out, cache, q_norm, k_norm, eps: float,
     _ok(_fn("attention_talking", "rg_talking_prepare")(
         _ptr(qkv), c_int(_dtype_code(qkv)), c_int(qkv.stride(0)), _ptr(q_out), _ptr(cache if slots is not None else None),
         _ptr(q_norm), _ptr(k_norm), c_float(eps), _ptr(freq), c_int(rot_dims), _ptr(positions), _ptr(slots), c_int(T),
-        c_int(H), c_int(G), c_int(d), c_int(dv), _ptr(qa), _ptr(talk), c_float(scale), _stream()), "talking_prepare")
+        c_int(H), c_int(G), c_int(d), c_int(dv), _ptr(qa), _ptr(talk), c_float(scale), _ptr(qc), _stream()), "talking_prepare")
+
+
+# Up to this many key numbers side by side the flash form is the faster one for prompts (measured on B200: at 128
+# 111 us against 168 for 2,048 tokens, at 256 455 against 427: that kernel holds one block per SM at head size 256).
+TALKING_FLASH_MAX_KEYS = 128
+
+
+def talking_flash_ok(dtype, G: int, d: int, dv: int) -> bool:
+    """Whether prompts of talking-heads attention can run on the flash kernel of paged attention: bfloat16, all key
+    heads side by side within the head sizes at which that kernel is the faster form, values no larger than that."""
+    return dtype == torch.bfloat16 and (G * d) % 16 == 0 and 16 <= G * d <= TALKING_FLASH_MAX_KEYS and dv <= G * d
+
+
+def talking_prefill_flash(qc: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, batch, G: int, d: int,
+                          dv: int, out: torch.Tensor, out_scale: float = 1.0) -> None:
+    """Talking-heads attention of the step's requests that bring several tokens, from mixed queries ``qc``
+    [T, H, G d]: their contexts are laid out as temporary key/value pages (every key/value head sees all key heads
+    side by side and its own values, zero-padded), the flash kernel of paged attention runs over them, and the
+    first ``dv`` numbers of every head's output, times ``out_scale``, go to those requests' rows of ``out``
+    [T, H dv] (rows may be further apart).  Causal, no window."""
+    _check(qc, "qc", torch.bfloat16)
+    _check(cache, "cache", torch.bfloat16)
+    T, H, Gd = qc.shape
+    if Gd != G * d or cache.dim() != 3 or cache.shape[2] != G * (d + dv) or not talking_flash_ok(qc.dtype, G, d, dv):
+        raise KernelError(f"talking_prefill_flash: queries {tuple(qc.shape)}, cache {tuple(cache.shape)}")
+    _check_out_view(out, T, H * dv, qc.dtype, "talking_prefill_flash")
+    n_req, MB = block_table.shape
+    page = cache.shape[1]
+    kv = torch.empty((n_req * MB, 2, G, page, Gd), dtype=cache.dtype, device=cache.device)
+    _ok(_fn("attention_talking", "rg_talking_pack_kv")(
+        _ptr(cache), _ptr(block_table), c_int(MB), _ptr(batch.cu_seqlens), _ptr(batch.context_lens), _ptr(kv),
+        c_int(_dtype_code(cache)), c_int(n_req), c_int(page), c_int(G), c_int(d), c_int(dv), _stream()), "talking_pack_kv")
+    table = torch.arange(n_req * MB, dtype=torch.int32, device=cache.device).view(n_req, MB)
+    wide = torch.empty((T, H * Gd), dtype=qc.dtype, device=qc.device)
+    prefill_attention(qc, H * Gd, wide, kv, table, batch.prefill_tiles, batch.positions, H, G, Gd, 0, 1.0)
+    _ok(_fn("attention_talking", "rg_talking_select")(
+        _ptr(wide), _ptr(out), c_int(out.stride(0)), c_float(out_scale), c_int(_dtype_code(wide)), _ptr(batch.cu_seqlens),
+        _ptr(batch.req_of_token), c_int(T), c_int(H), c_int(Gd), c_int(dv), _stream()), "talking_select")
 
 
 def _check_out_view(out, T: int, n: int, dtype, what: str):

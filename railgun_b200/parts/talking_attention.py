@@ -13,9 +13,12 @@ the form of attention over a latent cache: the mixing is linear in q, so the
 step mixes the queries instead of the scores (Q'_h holds, for every key/value
 head c, scale * sum over c's heads g of M[h, g] q_g), every head then scores
 the same cache rows, and the kernel of ``latent_attention`` does the rest,
-each head keeping the values of its own key/value head.  Everything else,
-and the whole 32-bit path, runs the general kernel, which mixes the scores
-themselves.
+each head keeping the values of its own key/value head.  Requests that bring
+several tokens run on the flash kernel of ordinary paged attention instead
+where all key heads side by side fit its head sizes: their contexts are laid
+out as temporary pages in which every key/value head sees all keys and its
+own values.  Everything else, and the whole 32-bit path, runs the general
+kernel, which mixes the scores themselves.
 
 Sizes and constants are parameters; the norm and the mixing can be left out,
 which gives plain grouped-query attention with separate key and value sizes.
@@ -96,14 +99,20 @@ class TalkingAttention(Mixer):
         table = batch.block_table[cache.group]
         R, D = G * dv, G * (d + dv)
         if dv % 2 == 0 and ops.latent_attention_mma_ok(qkv.dtype, H, R, D):
-            # the tensor-core form: mixed queries over the rows [values | keys]
-            qa = torch.empty((T, H, D), dtype=qkv.dtype, device=qkv.device)
+            # the tensor-core forms, both over mixed queries: requests that bring several tokens on the flash kernel
+            # of paged attention over temporary pages (where the sizes fit it, there is no window, and the pages of
+            # the step's contexts stay within a few times its tokens), single tokens over the rows [values | keys]
+            flash = (self.window == 0 and batch.num_prefill_tiles > 0 and ops.talking_flash_ok(qkv.dtype, G, d, dv)
+                     and table.shape[0] * table.shape[1] * cache.page_size <= max(8192, 4 * T))
+            rows_form = batch.decode_only or batch.num_decode_rows > 0 or not flash
+            qa = torch.empty((T, H, D), dtype=qkv.dtype, device=qkv.device) if rows_form else None
+            qc = torch.empty((T, H, G * d), dtype=qkv.dtype, device=qkv.device) if flash else None
             ops.talking_prepare(qkv, None, cache.kv, self.q_norm, self.k_norm, self.eps, self.freq, self.rot_dims,
-                                batch.positions, slots, H, G, d, dv, qa=qa, talk=self.talk, scale=self.scale)
+                                batch.positions, slots, H, G, d, dv, qa=qa, talk=self.talk, scale=self.scale, qc=qc)
             if out is None:
                 out = torch.empty((T, H * dv), dtype=qkv.dtype, device=qkv.device)
             args = (batch.req_of_token, batch.positions, R, self.window, 1.0)
-            more = dict(select=(dv, H // G), out_scale=out_scale)
+            more = dict(select=(dv, H // G), out_scale=out_scale, score_from=R)     # R = G dv zeros lead the queries
             reach = min(batch.max_context_len, self.window) if self.window else batch.max_context_len
             chunks = -(-H // 64)
             if batch.decode_only:
@@ -111,7 +120,9 @@ class TalkingAttention(Mixer):
                 ops.latent_attention_mma(qa, out, cache.kv, table, None, None, n, *args,
                                          ops.latent_decode_splits(n, chunks, reach), **more)
                 return out
-            if batch.num_prefill_tiles:
+            if flash:
+                ops.talking_prefill_flash(qc, cache.kv, table, batch, G, d, dv, out, out_scale)
+            elif batch.num_prefill_tiles:
                 ops.latent_attention_mma(qa, out, cache.kv, table, batch.prefill_tiles, None, batch.num_prefill_tiles,
                                          *args, **more)
             if batch.num_decode_rows:

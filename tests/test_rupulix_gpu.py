@@ -140,7 +140,7 @@ def test_talking_attention_kernel_alone(H, G, d, dv, page, window, dtype):
                     ops.latent_attention_mma(qa, wide[:, 8:8 + H * dv], dev(cache), dev(table), tiles, None,
                                              2 if portion > 1 else 1,
                                              dev(torch.zeros(portion, dtype=torch.int32)), dev(positions), G * dv, window,
-                                             1.0, splits, select=(dv, hpg), out_scale=0.5)
+                                             1.0, splits, select=(dv, hpg), out_scale=0.5, score_from=G * dv)
                     assert rel(wide[-1, 8:8 + H * dv].view(H, dv), ref * 0.5) < 3e-2, f"key {key}, tensor cores, {splits} shares"
                     assert float(wide[:, :8].abs().max()) == 0.0 and float(wide[:, 8 + H * dv:].abs().max()) == 0.0
 
