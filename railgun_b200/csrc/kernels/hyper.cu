@@ -75,7 +75,9 @@ __global__ void hyper_step_kernel(float* __restrict__ xs, const float* __restric
 template <int S, typename Y, typename O>
 static int hyper_launch(float* xs, const float* x0, const void* y, const float* mix, const float* outc, const float* inc,
                         const float* norm_w, float eps, void* out, int out_ld, int T, int W, cudaStream_t s) {
-    return rg_launch(hyper_step_kernel<S, Y, O>, dim3(T), dim3(HC_THREADS), (size_t)W * sizeof(float), s, 1, xs, x0,
+    // few rows: more threads per row, so that a thread's loads are few and all in flight at once
+    const int threads = T >= 512 ? HC_THREADS : min(1024, max(HC_THREADS, (W + 63) / 64 * 32));
+    return rg_launch(hyper_step_kernel<S, Y, O>, dim3(T), dim3(threads), (size_t)W * sizeof(float), s, 1, xs, x0,
                      (const Y*)y, mix, outc, inc, norm_w, eps, (O*)out, out_ld, W);
 }
 

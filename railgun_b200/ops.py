@@ -39,6 +39,16 @@ def _check(t: torch.Tensor, name: str, dtype=None) -> None:
         raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
 
 
+def _check_rows(t: torch.Tensor, name: str, dtype=None) -> None:
+    """Like ``_check`` for a matrix whose rows may be further apart than its width (a slice of columns)."""
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dim() != 2 or t.stride(1) != 1 or t.stride(0) < t.shape[1]:
+        raise KernelError(f"{name} must be a matrix with unit column stride")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
 def _ptr(t) -> c_void_p:
     return c_void_p(0 if t is None else t.data_ptr())
 
@@ -550,7 +560,7 @@ def talking_prepare(qkv: torch.Tensor, q_out, cache, q_norm, k_norm, eps: float,
     write).  ``qa`` [T, H, G dv + G d] (if given) receives the queries of the tensor-core form: zeros, then for
     every key/value head c the numbers ``scale`` * sum over the heads g of c of ``talk``[h, g] q_g; ``qc``
     [T, H, G d] (if given) the same without the zeros."""
-    _check(qkv, "qkv")
+    _check_rows(qkv, "qkv")
     if qc is not None:
         _check(qc, "qc", qkv.dtype)
         if qc.shape != (qkv.shape[0], H, G * d):
@@ -668,7 +678,7 @@ def recurrent_conv(proj: torch.Tensor, x_off: int, xb: torch.Tensor, taps: torch
     """u [T, C] float32: the causal convolution (``taps`` [C, K], bias ``cb``) of proj[:, x_off:x_off + C] + ``xb``
     per channel along each request's tokens, continued from the request's state slot (``state`` [slots, K, C]:
     rows 0..K-2 the last inputs) unless the request starts at position 0."""
-    _check(proj, "proj")
+    _check_rows(proj, "proj")
     for t, name in ((xb, "xb"), (taps, "taps"), (cb, "cb"), (state, "state")):
         _check(t, name, torch.float32)
     C, K = taps.shape
@@ -695,7 +705,7 @@ def recurrent_scan(proj: torch.Tensor, y_off: int, x_off: int, yb, xb, u: torch.
     [blocks, T, 2 bs] float32), from the request's state (row K-1 of its slot) or from zero at position 0;
     returns S_t gelu_tanh(proj[:, y_off:] + yb) times ``out_scale`` as [T, C] in proj's type, and leaves S and
     the convolution's last K-1 inputs in the slot."""
-    _check(proj, "proj")
+    _check_rows(proj, "proj")
     for t, name in ((yb, "yb"), (xb, "xb"), (u, "u"), (gates, "gates"), (rb, "rb"), (ib, "ib"), (lam, "lam"),
                     (state, "state")):
         _check(t, name, torch.float32)

@@ -66,21 +66,25 @@ class GatedRecurrence(Mixer):
         # both gates' matrices side by side, laid out for u_b @ [R_b^T | I_b^T]: [blocks, bs, 2 bs], 32-bit
         self.w_gates = torch.cat([f32("ra"), f32("ri")], dim=1).transpose(1, 2).contiguous()
         tensors.drop(b + "ra", b + "ri")
+        self.w_in = self.w_yx
         self.w_o = tensors.get(b + "o", env.dtype)
         self.out_features = self.C
 
-    def mix(self, x, batch, cache, writes=True, out=None, out_scale: float = 1.0):
+    def mix(self, x, batch, cache, writes=True, out=None, out_scale: float = 1.0, proj=None):
         """S g [T, width] times ``out_scale``, before the output product (into ``out`` if given).  The state
-        advances by the step's tokens."""
+        advances by the step's tokens.  ``proj``: x times ``w_in``, if the caller has it already (as columns
+        of a wider product)."""
         C, B, bs = self.C, self.B, self.bs
-        proj = ops.linear(x, self.w_yx)                                        # [T, 2 C] = gate branch | input branch
+        if proj is None:
+            proj = ops.linear(x, self.w_yx)                                    # [T, 2 C] = gate branch | input branch
         u = ops.recurrent_conv(proj, C, self.xb, self.taps, self.cb, cache.state, batch)
         gates = torch.bmm(u.view(-1, B, bs).transpose(0, 1), self.w_gates)     # [B, T, 2 bs] in true 32-bit
         return ops.recurrent_scan(proj, 0, C, self.yb, self.xb, u, gates, self.rb, self.ib, self.lam, self.decay,
                                   cache.state, batch, out, out_scale)
 
     def forward(self, x, batch, cache, writes=True):
-        return ops.linear(self.mix(x, batch, cache, writes), self.w_o)
+        w_o = self.w_o if self.w_o.is_contiguous() else self.w_o.contiguous()     # a share of a stacked matrix
+        return ops.linear(self.mix(x, batch, cache, writes), w_o)
 
 
 register_mixer("gated_recurrence", GatedRecurrence)

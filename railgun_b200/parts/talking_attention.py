@@ -79,6 +79,7 @@ class TalkingAttention(Mixer):
         b = self._base(p, prefix)
         self.w_qkv = torch.cat([tensors.get(b + n, env.dtype) for n in ("q", "k", "v")], dim=0).contiguous()
         tensors.drop(b + "q", b + "k", b + "v")
+        self.w_in = self.w_qkv
         self.w_o = tensors.get(b + "o", env.dtype)
         self.out_features = self.H * self.dv
         norm = p.get("qk_norm", True)
@@ -89,11 +90,12 @@ class TalkingAttention(Mixer):
         self.freq = tensors.shared_part(("rotary_frequencies", self.rot_dims, base),
                                         lambda: rotary_frequencies(self.rot_dims, base).to(env.device))
 
-    def mix(self, x, batch, cache, writes=True, out=None, out_scale: float = 1.0):
+    def mix(self, x, batch, cache, writes=True, out=None, out_scale: float = 1.0, proj=None):
         """The heads' outputs [T, heads * v_dim] times ``out_scale``, before the output product (into ``out``, a
-        view whose rows may be further apart, if given)."""
+        view whose rows may be further apart, if given).  ``proj``: x times ``w_in``, if the caller has it
+        already (as columns of a wider product)."""
         H, G, d, dv = self.H, self.G, self.d, self.dv
-        qkv = ops.linear(x, self.w_qkv)
+        qkv = proj if proj is not None else ops.linear(x, self.w_qkv)
         T = qkv.shape[0]
         slots = batch.slot_mapping[cache.group] if writes else None
         table = batch.block_table[cache.group]
@@ -137,7 +139,8 @@ class TalkingAttention(Mixer):
                                              self.window, self.scale, out, out_scale)
 
     def forward(self, x, batch, cache, writes=True):
-        return ops.linear(self.mix(x, batch, cache, writes), self.w_o)
+        w_o = self.w_o if self.w_o.is_contiguous() else self.w_o.contiguous()     # a share of a stacked matrix
+        return ops.linear(self.mix(x, batch, cache, writes), w_o)
 
 
 register_mixer("talking_attention", TalkingAttention)
