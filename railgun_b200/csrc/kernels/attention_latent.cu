@@ -102,12 +102,14 @@ extern "C" int rg_latent_rope_cache(const void* proj, int ld, int kv_off, void* 
     cudaStream_t s = (cudaStream_t)stream;
     const size_t cs_bytes = (size_t)((rot_dims > 0 ? rot_dims : 1) + (q_in_place ? H * dr : 0)) * sizeof(float);
     if (cs_bytes > 48 * 1024) return RG_ERR_UNSUPPORTED;
+    // few tokens: more threads per token, so that each phase's dependent loads are one round
+    const int rope_threads = T <= 256 ? 512 : LAT_THREADS;
     if (dtype == RG_DTYPE_BF16)
-        return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const bf16*)proj, ld,
+        return rg_launch(latent_rope_cache_kernel<bf16>, dim3(T), dim3(rope_threads), cs_bytes, s, 1, (const bf16*)proj, ld,
                          kv_off, (bf16*)qa, (bf16*)cache, norm_w, eps, freq, rot_dims, interleaved, positions, slots, H, dn, dr, R,
                          q_in_place ? (bf16*)proj : (bf16*)nullptr);
     if (dtype == RG_DTYPE_F32)
-        return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(LAT_THREADS), cs_bytes, s, 1, (const float*)proj, ld,
+        return rg_launch(latent_rope_cache_kernel<float>, dim3(T), dim3(rope_threads), cs_bytes, s, 1, (const float*)proj, ld,
                          kv_off, (float*)qa, (float*)cache, norm_w, eps, freq, rot_dims, interleaved, positions, slots, H, dn, dr, R,
                          q_in_place ? (float*)proj : (float*)nullptr);
     return RG_ERR_UNSUPPORTED;

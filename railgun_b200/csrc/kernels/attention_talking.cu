@@ -95,16 +95,14 @@ __global__ void talking_prepare_kernel(const A* __restrict__ qkv, int ld, A* __r
             qrow[(size_t)h * Dq + (e - h * Gdv)] = from_f32<A>(0.f);
         }
     }
-    for (int h = 0; h < H; ++h) {
+    for (int e = threadIdx.x; e < H * Gd; e += blockDim.x) {
+        const int h = e / Gd, j = e - h * Gd, c = j / d, i = j - c * d;
         const float* trow = tk + h * H;                      // M[h, :] in shared memory
-        for (int j = threadIdx.x; j < Gd; j += blockDim.x) {
-            const int c = j / d, i = j - c * d;
-            float v = 0.f;
-            if (talk) { for (int g = c * hpg; g < (c + 1) * hpg; ++g) v += trow[g] * qall[g * d + i]; }
-            else if (h / hpg == c) v = qall[h * d + i];
-            if (qa) qa[((size_t)t * H + h) * Dq + Gdv + j] = from_f32<A>(v * scale);
-            if (qc) qc[((size_t)t * H + h) * Gd + j] = from_f32<A>(v * scale);
-        }
+        float v = 0.f;
+        if (talk) { for (int g = c * hpg; g < (c + 1) * hpg; ++g) v += trow[g] * qall[g * d + i]; }
+        else if (h / hpg == c) v = qall[h * d + i];
+        if (qa) qa[((size_t)t * H + h) * Dq + Gdv + j] = from_f32<A>(v * scale);
+        if (qc) qc[((size_t)t * H + h) * Gd + j] = from_f32<A>(v * scale);
     }
 }
 
@@ -191,15 +189,20 @@ extern "C" int rg_talking_prepare(const void* qkv, int dtype, int ld, void* q_ou
     if (T <= 0) return 0;
     if (dims < 0 || dims > d || (dims & 1) || H < 1 || G < 1 || H % G || d < 1 || dv < 1 || (!q_out && !qa && !qc))
         return RG_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(dims + (TK_THREADS / 32) * d + ((qa || qc) ? H * d + H * H : 0)) * sizeof(float);
+    // a warp per head: as many warps as heads (up to 16), so that the heads' dependent loads overlap
+    int nwarp = H + G < 16 ? H + G : 16;
+    if (nwarp < 4) nwarp = 4;
+    while (nwarp > 4 && (size_t)(dims + nwarp * d + ((qa || qc) ? H * d + H * H : 0)) * sizeof(float) > 48 * 1024) --nwarp;
+    const size_t smem = (size_t)(dims + nwarp * d + ((qa || qc) ? H * d + H * H : 0)) * sizeof(float);
     if (smem > 48 * 1024) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    const int prep_threads = 32 * nwarp;
     if (dtype == RG_DTYPE_BF16)
-        return rg_launch(talking_prepare_kernel<bf16>, dim3(T), dim3(TK_THREADS), smem, s, 1, (const bf16*)qkv, ld,
+        return rg_launch(talking_prepare_kernel<bf16>, dim3(T), dim3(prep_threads), smem, s, 1, (const bf16*)qkv, ld,
                          (bf16*)q_out, (bf16*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv,
                          (bf16*)qa, talk, scale, (bf16*)qc);
     if (dtype == RG_DTYPE_F32)
-        return rg_launch(talking_prepare_kernel<float>, dim3(T), dim3(TK_THREADS), smem, s, 1, (const float*)qkv, ld,
+        return rg_launch(talking_prepare_kernel<float>, dim3(T), dim3(prep_threads), smem, s, 1, (const float*)qkv, ld,
                          (float*)q_out, (float*)cache, q_norm, k_norm, eps, freq, dims, positions, slots, H, G, d, dv,
                          (float*)qa, talk, scale, (float*)qc);
     return RG_ERR_UNSUPPORTED;
