@@ -909,12 +909,16 @@ def run_kernels(args):
             us_ = [ops.recurrent_conv(p, C, xb, taps, cb, state, batch) for p in projs]
             us_g = timed(lambda: [torch.bmm(u.view(-1, Bk, C // Bk).transpose(0, 1), wg) for u in us_])
             gs = [torch.bmm(u.view(-1, Bk, C // Bk).transpose(0, 1), wg) for u in us_]
+            # the same products from u as two bfloat16 numbers (what portions of a bfloat16 model run)
+            hv = [ops.recurrent_conv(p, C, xb, taps, cb, state, batch, halves_blocks=Bk)[1] for p in projs]
+            wh = torch.cat([wg.to(torch.bfloat16)] * 2, dim=1).contiguous()
+            us_h = timed(lambda: [torch.bmm(h.view(-1, Bk, 2 * C // Bk).transpose(0, 1), wh, out_dtype=torch.float32) for h in hv])
             us_s = timed(lambda: [ops.recurrent_scan(p, 0, C, yb, xb, u, g, rb, ib, lam, 8.0, state, batch)
                                   for p, u, g in zip(projs, us_, gs)])
             by_c, by_s = T * C * (2 + 4), T * C * (4 + 8 + 2 + 2)
             out(f"recurrence C{C} blocks{Bk} taps{K} T{T}", us_c + us_g + us_s, conv_us=round(us_c, 2),
                 conv_frac=round(by_c / us_c / 1e3 / pk["hbm_gbs"], 3), gates_product_us=round(us_g, 2),
-                gates_TFLOPs=round(2 * T * C * 2 * (C // Bk) / us_g / 1e6, 2), scan_us=round(us_s, 2),
+                gates_TFLOPs=round(2 * T * C * 2 * (C // Bk) / us_g / 1e6, 2), gates_product_bf16_halves_us=round(us_h, 2), scan_us=round(us_s, 2),
                 scan_frac=round(by_s / us_s / 1e3 / pk["hbm_gbs"], 3))
     if on("moe"):
         # the routed experts' two grouped products (32 experts of 1,024 at width 2,048, 4 choices) beside the dense

@@ -33,7 +33,8 @@ __global__ void recurrent_conv_kernel(const A* __restrict__ proj, int ld, int x_
                                       const float* __restrict__ taps, const float* __restrict__ cb,
                                       const float* __restrict__ state, const int* __restrict__ cu_seqlens,
                                       const int* __restrict__ req_of_token, const int* __restrict__ start_pos,
-                                      const int* __restrict__ slots, float* __restrict__ u, int C, int K) {
+                                      const int* __restrict__ slots, float* __restrict__ u, int C, int K,
+                                      bf16* __restrict__ halves, int bs) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x;
@@ -53,6 +54,15 @@ __global__ void recurrent_conv_kernel(const A* __restrict__ proj, int ld, int x_
         acc += taps[(size_t)c * K + (K - 1 - k)] * xin;
     }
     u[(size_t)t * C + c] = acc;
+    if (halves) {
+        // u as two bfloat16 numbers, u = hi + lo to 2^-17: [T, blocks, 2, bs], for a tensor-core product with
+        // 32-bit accumulation that is as good as a 32-bit one
+        const int blk = c / bs, i = c - blk * bs;
+        const bf16 hi = __float2bfloat16_rn(acc);
+        bf16* dst = halves + ((size_t)t * (C / bs) + blk) * 2 * bs + i;
+        dst[0] = hi;
+        dst[bs] = __float2bfloat16_rn(acc - __bfloat162float(hi));
+    }
 }
 
 // gates [blocks, T, 2 bs] float: R_b u_b | I_b u_b.  out [T, C] rows out_ld apart, times out_scale.
@@ -236,17 +246,18 @@ __global__ void recurrent_finish_kernel(const A* __restrict__ proj, int ld, int 
 
 extern "C" int rg_recurrent_conv(const void* proj, int dtype, int ld, int x_off, const float* xb, const float* taps,
                                  const float* cb, const float* state, const int* cu_seqlens, const int* req_of_token,
-                                 const int* start_pos, const int* slots, float* u, int T, int C, int K, void* stream) {
+                                 const int* start_pos, const int* slots, float* u, int T, int C, int K, void* halves,
+                                 int bs, void* stream) {
     if (T <= 0) return 0;
-    if (C < 1 || K < 1 || K > REC_MAX_TAPS) return RG_ERR_UNSUPPORTED;
+    if (C < 1 || K < 1 || K > REC_MAX_TAPS || (halves && (bs < 1 || C % bs))) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, (C + REC_THREADS - 1) / REC_THREADS);
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(recurrent_conv_kernel<bf16>, grid, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, x_off, xb,
-                         taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K);
+                         taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K, (bf16*)halves, bs);
     if (dtype == RG_DTYPE_F32)
         return rg_launch(recurrent_conv_kernel<float>, grid, dim3(REC_THREADS), 0, s, 1, (const float*)proj, ld, x_off, xb,
-                         taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K);
+                         taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K, (bf16*)halves, bs);
     return RG_ERR_UNSUPPORTED;
 }
 

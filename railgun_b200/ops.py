@@ -674,10 +674,12 @@ def talking_attention_general(q: torch.Tensor, cache: torch.Tensor, talk, block_
 
 
 def recurrent_conv(proj: torch.Tensor, x_off: int, xb: torch.Tensor, taps: torch.Tensor, cb: torch.Tensor,
-                   state: torch.Tensor, batch) -> torch.Tensor:
+                   state: torch.Tensor, batch, halves_blocks: int = 0):
     """u [T, C] float32: the causal convolution (``taps`` [C, K], bias ``cb``) of proj[:, x_off:x_off + C] + ``xb``
     per channel along each request's tokens, continued from the request's state slot (``state`` [slots, K, C]:
-    rows 0..K-2 the last inputs) unless the request starts at position 0."""
+    rows 0..K-2 the last inputs) unless the request starts at position 0.  With ``halves_blocks`` = B > 0 also
+    returns u as two bfloat16 numbers per element, u = hi + lo to 2^-17, laid out [T, B, 2, C / B] (per block of
+    channels the hi numbers, then the lo numbers): (u, halves)."""
     _check_rows(proj, "proj")
     for t, name in ((xb, "xb"), (taps, "taps"), (cb, "cb"), (state, "state")):
         _check(t, name, torch.float32)
@@ -686,11 +688,17 @@ def recurrent_conv(proj: torch.Tensor, x_off: int, xb: torch.Tensor, taps: torch
     if state.shape[1:] != (K, C) or proj.shape[1] < x_off + C or xb.numel() != C or cb.numel() != C:
         raise KernelError("recurrent_conv: sizes do not match")
     u = torch.empty((T, C), dtype=torch.float32, device=proj.device)
+    halves = None
+    if halves_blocks:
+        if C % halves_blocks:
+            raise KernelError(f"recurrent_conv: {C} channels do not split into {halves_blocks} blocks")
+        halves = torch.empty((T, halves_blocks, 2, C // halves_blocks), dtype=torch.bfloat16, device=proj.device)
     _ok(_fn("recurrent", "rg_recurrent_conv")(
         _ptr(proj), c_int(_dtype_code(proj)), c_int(proj.stride(0)), c_int(x_off), _ptr(xb), _ptr(taps), _ptr(cb),
         _ptr(state), _ptr(batch.cu_seqlens), _ptr(batch.req_of_token), _ptr(batch.start_pos), _ptr(batch.state_slots),
-        _ptr(u), c_int(T), c_int(C), c_int(K), _stream()), "recurrent_conv")
-    return u
+        _ptr(u), c_int(T), c_int(C), c_int(K), _ptr(halves), c_int(C // halves_blocks if halves_blocks else 0),
+        _stream()), "recurrent_conv")
+    return (u, halves) if halves_blocks else u
 
 
 # Steps whose longest portion is at most this many tokens compute gates and recurrence in one kernel.
