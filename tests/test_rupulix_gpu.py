@@ -39,7 +39,7 @@ def dev(x, dtype=None):
 # ---- hyper-connections alone ------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("S,W,T", [(1, 24, 3), (2, 64, 5), (3, 100, 9), (4, 256, 300), (8, 40, 2)])
+@pytest.mark.parametrize("S,W,T", [(1, 24, 3), (2, 64, 5), (3, 100, 9), (4, 256, 300), (8, 40, 2), (2, 128, 700), (3, 36, 513)])
 def test_hyper_step_alone(S, W, T, dtype):
     """The start (all copies the same), an update fused with the next read, and the fold into one stream."""
     from railgun_b200 import ops
@@ -306,6 +306,31 @@ def test_recurrence_remembers_far_tokens_through_many_single_steps():
     assert np.abs(ref[-1] - without[-1]).max() > 0.3 * np.abs(ref[-1]).max()              # the first token matters
     got = feed_part(runner, mixer, view, h.to(DEV), tuple(range(1, 400)))
     assert rel(got, ref) < 3e-5 and rel(got[-1], ref[-1]) < 3e-5
+
+
+def test_convolution_continues_from_the_state_and_splits_u_into_two_halves():
+    """The convolution of two requests side by side (one new, one that continues from its slot's tail), and u as
+    two bfloat16 numbers whose sum is u to 2^-16: what the gates' tensor-core products are fed."""
+    from types import SimpleNamespace
+    from railgun_b200 import ops
+    rng = np.random.default_rng(3)
+    C, K, B, n0, n1 = 48, 4, 3, 5, 7
+    proj = torch.tensor(rng.normal(size=(n0 + n1, 2 * C)), dtype=torch.bfloat16)
+    xb, cb = rng.normal(size=C) * 0.3, rng.normal(size=C) * 0.3
+    taps = rng.normal(size=(C, K))
+    state = torch.tensor(rng.normal(size=(3, K, C)), dtype=torch.float32)
+    batch = SimpleNamespace(cu_seqlens=dev(torch.tensor([0, n0, n0 + n1], dtype=torch.int32)),
+                            req_of_token=dev(torch.tensor([0] * n0 + [1] * n1, dtype=torch.int32)),
+                            start_pos=dev(torch.tensor([0, 9], dtype=torch.int32)),
+                            state_slots=dev(torch.tensor([2, 1], dtype=torch.int32)))
+    u, halves = ops.recurrent_conv(dev(proj), C, dev(xb, torch.float32), dev(taps, torch.float32), dev(cb, torch.float32),
+                                   dev(state), batch, halves_blocks=B)
+    xin = proj.double().numpy()[:, C:] + xb
+    ref0 = P.causal_conv(xin[:n0], taps, cb)                                              # starts from zeros
+    ref1 = P.causal_conv(np.concatenate([state[1, :K - 1].double().numpy(), xin[n0:]]), taps, cb)[K - 1:]
+    assert rel(u, np.concatenate([ref0, ref1])) < 2e-6
+    both = halves.float().view(n0 + n1, B, 2, C // B)
+    assert rel((both[:, :, 0] + both[:, :, 1]).reshape(n0 + n1, C), u) < 2e-5
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
