@@ -138,6 +138,89 @@ __global__ void recurrent_gate_kernel(const float* __restrict__ u, const float* 
     b_out[(size_t)t * C + c] = sqrtf(-expm1f(2.f * log_a)) * rec_sigmoid(g[bs] + bic) * u[(size_t)t * C + c];
 }
 
+
+// Four channels per thread with 16-byte accesses (C, bs, x_off and ld multiples of 4, 16-byte aligned bases): the
+// same arithmetic as recurrent_conv_kernel and recurrent_gate_kernel, for steps of many tokens.
+__device__ __forceinline__ float4 rec_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 rec_load4(const bf16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void rec_store4(bf16* p, float4 v) {
+    uint2 o;
+    *reinterpret_cast<__nv_bfloat162*>(&o.x) = __floats2bfloat162_rn(v.x, v.y);
+    *reinterpret_cast<__nv_bfloat162*>(&o.y) = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2*>(p) = o;
+}
+
+template <typename A>
+__global__ void recurrent_conv_vec4_kernel(const A* __restrict__ proj, int ld, int x_off, const float* __restrict__ xb,
+                                           const float* __restrict__ taps, const float* __restrict__ cb,
+                                           const float* __restrict__ state, const int* __restrict__ cu_seqlens,
+                                           const int* __restrict__ req_of_token, const int* __restrict__ start_pos,
+                                           const int* __restrict__ slots, float* __restrict__ u, int C, int K,
+                                           bf16* __restrict__ halves, int bs) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+    if (c >= C) return;
+    const int r = req_of_token[t];
+    const int i = t - cu_seqlens[r];
+    const int slot = slots[r];
+    const bool has_past = slot >= 0 && start_pos[r] > 0;
+    const float4 b = rec_load4(xb + c);
+    float4 acc = rec_load4(cb + c);
+    const float* tp = taps + (size_t)c * K;                    // four channels' taps, K each
+    for (int k = 0; k < K; ++k) {
+        const int idx = i - k;
+        float4 xin;
+        if (idx >= 0) {
+            xin = rec_load4(proj + (size_t)(t - k) * ld + x_off + c);
+            xin.x += b.x; xin.y += b.y; xin.z += b.z; xin.w += b.w;
+        } else if (has_past) {
+            xin = rec_load4(state + ((size_t)slot * K + (K - 1 + idx)) * C + c);
+        } else {
+            xin = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        const int j = K - 1 - k;
+        acc.x += tp[j] * xin.x; acc.y += tp[K + j] * xin.y; acc.z += tp[2 * K + j] * xin.z; acc.w += tp[3 * K + j] * xin.w;
+    }
+    *reinterpret_cast<float4*>(u + (size_t)t * C + c) = acc;
+    if (halves) {
+        const int blk = c / bs, o = c - blk * bs;
+        bf16* dst = halves + ((size_t)t * (C / bs) + blk) * 2 * bs + o;
+        const float4 hi = make_float4(__bfloat162float(__float2bfloat16_rn(acc.x)), __bfloat162float(__float2bfloat16_rn(acc.y)),
+                                      __bfloat162float(__float2bfloat16_rn(acc.z)), __bfloat162float(__float2bfloat16_rn(acc.w)));
+        rec_store4(dst, hi);
+        rec_store4(dst + bs, make_float4(acc.x - hi.x, acc.y - hi.y, acc.z - hi.z, acc.w - hi.w));
+    }
+}
+
+__global__ void recurrent_gate_vec4_kernel(const float* __restrict__ u, const float* __restrict__ gates,
+                                           const float* __restrict__ rb, const float* __restrict__ ib,
+                                           const float* __restrict__ lam, float decay, float* __restrict__ a_out,
+                                           float* __restrict__ b_out, int T, int C, int bs) {
+    const int t = blockIdx.x;
+    const int c = 4 * (blockIdx.y * blockDim.x + threadIdx.x);
+    if (c >= C) return;
+    const float4 l4 = rec_load4(lam + c), br = rec_load4(rb + c), bi = rec_load4(ib + c);
+    pdl_wait();
+    pdl_trigger();
+    const int blk = c / bs, o = c - blk * bs;
+    const float* g = gates + ((size_t)blk * T + t) * 2 * bs + o;
+    const float4 gr = rec_load4(g), gi = rec_load4(g + bs), uu = rec_load4(u + (size_t)t * C + c);
+    float4 a, b;
+#define REC_ONE(f) { const float log_a = -decay * rec_softplus(l4.f) * rec_sigmoid(gr.f + br.f); a.f = expf(log_a); \
+                     b.f = sqrtf(-expm1f(2.f * log_a)) * rec_sigmoid(gi.f + bi.f) * uu.f; }
+    REC_ONE(x) REC_ONE(y) REC_ONE(z) REC_ONE(w)
+#undef REC_ONE
+    *reinterpret_cast<float4*>(a_out + (size_t)t * C + c) = a;
+    *reinterpret_cast<float4*>(b_out + (size_t)t * C + c) = b;
+}
+
 #define REC_AHEAD 8
 #define REC_CHUNK 64
 // The recurrence is associative, so a request's tokens are cut into chunks of REC_CHUNK that run side by side.
@@ -252,6 +335,18 @@ extern "C" int rg_recurrent_conv(const void* proj, int dtype, int ld, int x_off,
     if (C < 1 || K < 1 || K > REC_MAX_TAPS || (halves && (bs < 1 || C % bs))) return RG_ERR_UNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(T, (C + REC_THREADS - 1) / REC_THREADS);
+    const bool vec4 = T >= 64 && C % 4 == 0 && ld % 4 == 0 && x_off % 4 == 0 && (!halves || bs % 4 == 0) &&
+                      ((uintptr_t)proj | (uintptr_t)xb | (uintptr_t)taps | (uintptr_t)cb | (uintptr_t)state | (uintptr_t)u |
+                       (uintptr_t)halves) % 16 == 0;
+    if (vec4) {
+        dim3 g4(T, (C / 4 + REC_THREADS - 1) / REC_THREADS);
+        if (dtype == RG_DTYPE_BF16)
+            return rg_launch(recurrent_conv_vec4_kernel<bf16>, g4, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, x_off,
+                             xb, taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K, (bf16*)halves, bs);
+        if (dtype == RG_DTYPE_F32)
+            return rg_launch(recurrent_conv_vec4_kernel<float>, g4, dim3(REC_THREADS), 0, s, 1, (const float*)proj, ld,
+                             x_off, xb, taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K, (bf16*)halves, bs);
+    }
     if (dtype == RG_DTYPE_BF16)
         return rg_launch(recurrent_conv_kernel<bf16>, grid, dim3(REC_THREADS), 0, s, 1, (const bf16*)proj, ld, x_off, xb,
                          taps, cb, state, cu_seqlens, req_of_token, start_pos, slots, u, C, K, (bf16*)halves, bs);
@@ -276,7 +371,13 @@ extern "C" int rg_recurrent_scan(const void* proj, int dtype, int ld, int y_off,
         float* a_buf = ab;
         float* b_buf = ab + (size_t)T * C;
         if (max_tokens < 1 || R > 65535 || grid.y > 65535) return RG_ERR_UNSUPPORTED;
-        int e = rg_launch(recurrent_gate_kernel, dim3(T, grid.y), dim3(REC_THREADS), 0, s, 1, u, gates, rb, ib, lam, decay,
+        int e;
+        if (bs % 4 == 0 && ((uintptr_t)u | (uintptr_t)gates | (uintptr_t)rb | (uintptr_t)ib | (uintptr_t)lam | (uintptr_t)ab) % 16 == 0 &&
+            ((size_t)T * C) % 4 == 0)
+            e = rg_launch(recurrent_gate_vec4_kernel, dim3(T, (C / 4 + REC_THREADS - 1) / REC_THREADS), dim3(REC_THREADS), 0, s, 1,
+                          u, gates, rb, ib, lam, decay, a_buf, b_buf, T, C, bs);
+        else
+            e = rg_launch(recurrent_gate_kernel, dim3(T, grid.y), dim3(REC_THREADS), 0, s, 1, u, gates, rb, ib, lam, decay,
                           a_buf, b_buf, T, C, bs);
         if (e) return e;
         dim3 cgrid((max_tokens + REC_CHUNK - 1) / REC_CHUNK, R, grid.y);
